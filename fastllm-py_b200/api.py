@@ -55,7 +55,13 @@ class Model:
         torch.cuda.set_device(dev)
         dtype = getattr(torch, engine_config.dtype)
         names = None if isinstance(store, _RandomSpec) else set(store.names())
-        plan = arch.make_plan(config, names)
+        import inspect
+        if "tensor_shapes" in inspect.signature(arch.make_plan).parameters:
+            # an architecture some of whose sizes only the checkpoint's tensors give
+            shapes = None if names is None else {n: tuple(store.describe(n)[0]) for n in names}
+            plan = arch.make_plan(config, names, tensor_shapes=shapes)
+        else:
+            plan = arch.make_plan(config, names)
         max_len = engine_config.max_model_len or plan.max_positions
         ctx = BuildContext(dev, dtype, engine_config.page_size, max_len)
         decoder = Decoder(plan, ctx)

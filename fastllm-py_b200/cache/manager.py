@@ -192,14 +192,17 @@ class CacheManager:
                 continue
             # The next query sits at position seq_len and sees keys from
             # seq_len - window + 1 on; pages wholly below that are dead.
+            # A need that keeps the sequence's first tokens holds on to the pages they lie in.
             first_needed = rc.seq_len - g.window + 1
             row = rc.pages[gi]
             dead_pages = min(max(0, first_needed) // self.page_size, len(row))
-            if dead_pages > rc.released[gi]:
-                self._give_back(g, row[rc.released[gi]:dead_pages])
-                for i in range(rc.released[gi], dead_pages):
+            kept_pages = self._pages_for(int(getattr(g.need, "keep_first", 0) or 0))
+            done = max(rc.released[gi], kept_pages)
+            if dead_pages > done:
+                self._give_back(g, row[done:dead_pages])
+                for i in range(done, dead_pages):
                     row[i] = -1
-                rc.tables[gi][rc.released[gi]:dead_pages] = -1
+                rc.tables[gi][done:dead_pages] = -1
                 rc.version += 1
                 rc.released[gi] = dead_pages
 

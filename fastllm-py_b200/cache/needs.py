@@ -17,12 +17,15 @@ from dataclasses import dataclass
 class PagedNeed:
     """Per-token storage in pages.  Subclasses are frozen dataclasses (equal needs share a
     group of pages) with an attribute `window` (None: every token is kept; a number: the
-    last `window` tokens, the query's own position included, so older pages can go back) and
+    last `window` tokens, the query's own position included, so older pages can go back),
+    optionally `keep_first` (with a window: the sequence's first so many tokens stay as
+    well, so the pages that hold them never go back) and
 
         page_shape(page_size) -> tuple   shape of one page of one layer, in elements
         dtype                            "activation" (the engine's activation dtype) or a torch dtype name
     """
     window = None
+    keep_first = 0
     dtype = "activation"
 
     def page_shape(self, page_size: int) -> tuple:
@@ -83,6 +86,7 @@ class PagedKeysValues(PagedNeed):
     key_dim: int
     value_dim: int
     window: int | None = None
+    keep_first: int = 0
 
     def page_shape(self, page_size: int) -> tuple:
         return (self.kv_heads, page_size, self.key_dim + self.value_dim)

@@ -1,0 +1,200 @@
+// Kernels of the post-norm block with a short input convolution and a gated residual, and of the
+// embedding with a hashed table of token pairs.
+//
+// The block: a sublayer reads the residual stream x itself (no norm in front), through a causal
+// convolution over time on every channel; its result is gated, normed and added:
+//     h  = x                       hc_t = h_t + sum_j w[:, j] h_(t - taps + 1 + j)      (zeros before position 0)
+//     y  = sublayer(hc) * sigmoid(W_g h + b_g)
+//     x <- x + y / sqrt(mean(y^2) + eps) * w_out
+// The last taps - 1 rows h of a request are its state, kept by position: ring[(position) mod (taps - 1)].
+//
+//   input_conv       per token: h (x in the activation type) and hc; rows before the step's first come from the ring
+//   gated_norm_add   per token: the gate, the norm and the add; also files the row's x (as it was before the add:
+//                    the input the sublayer's convolution saw) into the ring when it is among the request's last
+//                    taps - 1 rows of the step.  It runs after every reader of the ring in this step, so the ring is
+//                    never read and written by one launch
+//   sigmoid_gate     a[t, i] *= sigmoid(g[t, i])  (an output gate inside a mixer)
+//   pair_embed       x[t] = table[id_t] * scale + pairs[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets], row
+//                    `buckets` for a request's first token; the token before a step's first is per-request state,
+//                    read and rewritten by the block of the request's first row only
+//
+// All arithmetic is float; the residual stream is float in both precisions.
+#include "common.cuh"
+
+template <typename TO>
+__global__ void __launch_bounds__(256) input_conv_kernel(
+    const float* __restrict__ x, long x_ld, const float* __restrict__ w, int taps, const float* __restrict__ ring,
+    long ring_slot_stride, const int* __restrict__ positions, const int* __restrict__ tok_req,
+    const int* __restrict__ req_start, const int* __restrict__ req_slot, TO* __restrict__ h, long h_ld,
+    TO* __restrict__ hc, long hc_ld, int width) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int r = tok_req[t];
+    const int pos = positions[t], start = req_start[r];
+    const int back = taps - 1;
+    const float* ring_r = ring != nullptr ? ring + (long)req_slot[r] * ring_slot_stride : nullptr;
+    const float* xr = x + (long)t * x_ld;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float xi = xr[i];
+        float acc = 0.0f;
+        for (int j = 0; j < taps; ++j) {
+            const int k = back - j;                        // rows back in time
+            float v;
+            if (k == 0) v = xi;
+            else if (pos - k < 0) v = 0.0f;
+            else if (t - k >= start) v = x[(long)(t - k) * x_ld + i];
+            else v = ring_r[(long)((pos - k) % back) * width + i];
+            acc = __fmaf_rn(w[(long)i * taps + j], v, acc);
+        }
+        if (h != nullptr) h[(long)t * h_ld + i] = from_f32<TO>(xi);
+        hc[(long)t * hc_ld + i] = from_f32<TO>(xi + acc);
+    }
+}
+
+// w: [width, taps] float; ring: [slots, >= (taps - 1) * width] float (may be null when taps == 1).
+FL_API int fl_input_conv(const float* x, long x_ld, const float* w, int taps, const float* ring, long ring_slot_stride,
+                         const int* positions, const int* tok_req, const int* req_start, const int* req_slot, void* h,
+                         long h_ld, void* hc, long hc_ld, int out_dtype, int n_tokens, int width, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (taps < 1 || (taps > 1 && ring == nullptr)) return (int)cudaErrorInvalidValue;
+    FL_DISPATCH(out_dtype, TO, return fl_launch(input_conv_kernel<TO>, dim3(n_tokens), dim3(256), 0, stream, x, x_ld, w, taps,
+                                                ring, ring_slot_stride, positions, tok_req, req_start, req_slot, (TO*)h,
+                                                h_ld, (TO*)hc, hc_ld, width));
+    return 0;
+}
+
+template <typename TD>
+__global__ void __launch_bounds__(256) gated_norm_add_kernel(
+    float* __restrict__ x, long x_ld, const TD* __restrict__ y, long y_ld, const TD* __restrict__ gate, long gate_ld,
+    const float* __restrict__ gate_bias, const float* __restrict__ w, float eps, int width, float* __restrict__ ring,
+    long ring_slot_stride, int taps, const int* __restrict__ positions, const int* __restrict__ tok_req,
+    const int* __restrict__ req_start, const int* __restrict__ req_qlen, const int* __restrict__ req_slot) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float gated_row[];                   // [width]
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    const TD* yr = y + (long)t * y_ld;
+    const TD* gr = gate != nullptr ? gate + (long)t * gate_ld : nullptr;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = to_f32<TD>(yr[i]);
+        if (gr != nullptr) {
+            const float g = to_f32<TD>(gr[i]) + (gate_bias != nullptr ? gate_bias[i] : 0.0f);
+            v = v / (1.0f + expf(-g));
+        }
+        gated_row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)width + eps);
+    float* xr = x + (long)t * x_ld;
+    float* file = nullptr;
+    if (ring != nullptr && taps > 1) {
+        const int r = tok_req[t];
+        if (t >= req_start[r] + req_qlen[r] - (taps - 1))
+            file = ring + (long)req_slot[r] * ring_slot_stride + (long)(positions[t] % (taps - 1)) * width;
+    }
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float xi = xr[i];
+        if (file != nullptr) file[i] = xi;
+        xr[i] = xi + gated_row[i] * inv * w[i];
+    }
+}
+
+// gate may be null (no gate); ring may be null (nothing to file).
+FL_API int fl_gated_norm_add(float* x, long x_ld, const void* y, long y_ld, const void* gate, long gate_ld, int dtype,
+                             const float* gate_bias, const float* w, float eps, int n_tokens, int width, float* ring,
+                             long ring_slot_stride, int taps, const int* positions, const int* tok_req,
+                             const int* req_start, const int* req_qlen, const int* req_slot, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    FL_DISPATCH(dtype, TD, {
+        if (smem > 48 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(gated_norm_add_kernel<TD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        return fl_launch(gated_norm_add_kernel<TD>, dim3(n_tokens), dim3(256), smem, stream, x, x_ld, (const TD*)y, y_ld,
+                         (const TD*)gate, gate_ld, gate_bias, w, eps, width, ring, ring_slot_stride, taps, positions,
+                         tok_req, req_start, req_qlen, req_slot);
+    });
+    return 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) sigmoid_gate_kernel(T* __restrict__ a, long a_ld, const T* __restrict__ g, long g_ld,
+                                                           int cols) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    T* ar = a + (long)t * a_ld;
+    const T* gr = g + (long)t * g_ld;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x)
+        ar[i] = from_f32<T>(to_f32<T>(ar[i]) / (1.0f + expf(-to_f32<T>(gr[i]))));
+}
+
+FL_API int fl_sigmoid_gate(void* a, long a_ld, const void* g, long g_ld, int dtype, int n_rows, int cols,
+                           cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    FL_DISPATCH(dtype, T, return fl_launch(sigmoid_gate_kernel<T>, dim3(n_rows), dim3(256), 0, stream, (T*)a, a_ld,
+                                           (const T*)g, g_ld, cols));
+    return 0;
+}
+
+__device__ __forceinline__ int fed_token(int id, const int* fed, int n_fed) {
+    return (id < 0 && fed != nullptr && -1 - id < n_fed) ? fed[-1 - id] : id;
+}
+
+template <typename TT>
+__global__ void __launch_bounds__(256) pair_embed_kernel(
+    const TT* __restrict__ table, long table_ld, const TT* __restrict__ pairs, long pairs_ld, const int* __restrict__ ids,
+    float* __restrict__ out, long out_ld, int hidden, int vocab, int buckets, long mul_prev, long mul_cur, float scale,
+    const int* __restrict__ tok_req, const int* __restrict__ req_start, const int* __restrict__ req_ctx,
+    const int* __restrict__ req_qlen, const int* __restrict__ req_slot, int* __restrict__ last_token,
+    int* __restrict__ status, const int* __restrict__ fed, int n_fed) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ int before;
+    const int t = blockIdx.x;
+    const int r = tok_req[t], start = req_start[r];
+    const int id = fed_token(ids[t], fed, n_fed);
+    if (threadIdx.x == 0) {
+        if (t > start) {
+            before = fed_token(ids[t - 1], fed, n_fed);
+        } else {                                           // the request's first row of the step: the state is this block's
+            int* kept = last_token + req_slot[r];
+            before = req_ctx[r] > 0 ? *kept : -1;
+            *kept = fed_token(ids[start + req_qlen[r] - 1], fed, n_fed);
+        }
+    }
+    __syncthreads();
+    float* o = out + (long)t * out_ld;
+    const int prev = before;
+    if (id < 0 || id >= vocab || prev >= vocab) {
+        if (threadIdx.x == 0) atomicCAS(status, 0, t + 1);
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.0f;
+        return;
+    }
+    const long pair_row = prev < 0 ? (long)buckets : ((long)prev * mul_prev + (long)id * mul_cur) % (long)buckets;
+    const TT* row = table + (long)id * table_ld;
+    const TT* prow = pairs + pair_row * pairs_ld;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+        o[i] = to_f32<TT>(row[i]) * scale + to_f32<TT>(prow[i]);
+}
+
+// pairs: [buckets + 1, hidden]; last_token: [slots] int.
+FL_API int fl_pair_embed(const void* table, long table_ld, const void* pairs, long pairs_ld, int dtype, const int* ids,
+                         float* out, long out_ld, int n_tokens, int hidden, int vocab, int buckets, long mul_prev,
+                         long mul_cur, float scale, const int* tok_req, const int* req_start, const int* req_ctx,
+                         const int* req_qlen, const int* req_slot, int* last_token, int* status, const int* fed, int n_fed,
+                         cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (buckets < 1) return (int)cudaErrorInvalidValue;
+    FL_DISPATCH(dtype, TT, return fl_launch(pair_embed_kernel<TT>, dim3(n_tokens), dim3(256), 0, stream, (const TT*)table,
+                                            table_ld, (const TT*)pairs, pairs_ld, ids, out, out_ld, hidden, vocab, buckets,
+                                            mul_prev, mul_cur, scale, tok_req, req_start, req_ctx, req_qlen, req_slot,
+                                            last_token, status, fed, n_fed));
+    return 0;
+}

@@ -9,7 +9,8 @@
 //
 //   latent_prep       per token: rotary encoding of the queries' rotated parts, written behind where q~'s
 //                     first part will go; the latent normed and, with the rotated key part, written into
-//                     the token's cache row
+//                     the token's cache row.  Rotary pairs are (i, i + rot/2), or with `interleaved`
+//                     (2i, 2i + 1); pair i turns by the table's column i either way
 //   latent_attention  per (token, head): softmax over the visible rows (a window, if the layer has one),
 //                     keys walked in tiles of 128 aligned to absolute positions
 //
@@ -19,10 +20,11 @@
 #define LAT_TILE 128
 #define LAT_MAX_ACC 8            // value elements per thread: rank <= LAT_TILE * LAT_MAX_ACC
 
-// proj row: heads x [dim plain | rot rotated] queries, then (has_kv) rank latent + rot key elements.
+// proj row: heads x [dim plain | rot rotated] queries; kv row (has_kv): rank latent + rot key elements.
 template <typename T, typename TW, typename TQ>
 __global__ void __launch_bounds__(256) latent_prep_kernel(
-    const T* __restrict__ proj, long ld, TQ* __restrict__ q_out, long q_ld, int heads, int dim, int rot, int rank,
+    const T* __restrict__ proj, long ld, const T* __restrict__ kv_src, long kv_ld, int interleaved,
+    TQ* __restrict__ q_out, long q_ld, int heads, int dim, int rot, int rank,
     const TW* __restrict__ norm_w, float eps,
     const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int* __restrict__ positions,
     const int* __restrict__ slots, T* __restrict__ cache, int has_kv) {
@@ -40,12 +42,13 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(
         const int h = idx / half, i = idx % half;
         const T* p = row + (long)h * (dim + rot) + dim;
         TQ* o = q_row + (long)h * (rank + rot) + rank;
-        const float u = to_f32<T>(p[i]), v = to_f32<T>(p[i + half]);
-        o[i] = from_f32<TQ>(u * cs[i] - v * sn[i]);
-        o[i + half] = from_f32<TQ>(v * cs[i] + u * sn[i]);
+        const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+        const float u = to_f32<T>(p[a]), v = to_f32<T>(p[b]);
+        o[a] = from_f32<TQ>(u * cs[i] - v * sn[i]);
+        o[b] = from_f32<TQ>(v * cs[i] + u * sn[i]);
     }
     if (!has_kv) return;
-    const T* kv = row + (long)heads * (dim + rot);
+    const T* kv = kv_src + (long)t * kv_ld;
     T* dst = cache + (long)slots[t] * (rank + rot);
     float ss = 0.0f;
     for (int i = tid; i < rank; i += blockDim.x) {
@@ -56,9 +59,10 @@ __global__ void __launch_bounds__(256) latent_prep_kernel(
     const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
     for (int i = tid; i < rank; i += blockDim.x) dst[i] = from_f32<T>(to_f32<T>(kv[i]) * inv * to_f32<TW>(norm_w[i]));
     for (int i = tid; i < half; i += blockDim.x) {
-        const float u = to_f32<T>(kv[rank + i]), v = to_f32<T>(kv[rank + i + half]);
-        dst[rank + i] = from_f32<T>(u * cs[i] - v * sn[i]);
-        dst[rank + i + half] = from_f32<T>(v * cs[i] + u * sn[i]);
+        const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+        const float u = to_f32<T>(kv[rank + a]), v = to_f32<T>(kv[rank + b]);
+        dst[rank + a] = from_f32<T>(u * cs[i] - v * sn[i]);
+        dst[rank + b] = from_f32<T>(v * cs[i] + u * sn[i]);
     }
 }
 
@@ -127,14 +131,20 @@ __global__ void __launch_bounds__(LAT_TILE) latent_attention_kernel(
 }
 
 // q_out: [n_tokens, q_ld] (float or bfloat16), heads x [rank | rot]: the rot columns of every head are written here.
-FL_API int fl_latent_prep(const void* proj, int dtype, long ld, void* q_out, int q_dtype, long q_ld, int n_tokens, int heads, int dim,
+// kv: [n_tokens, kv_ld] rows of rank latent + rot key elements (null: they follow the queries in `proj`'s rows).
+FL_API int fl_latent_prep(const void* proj, int dtype, long ld, const void* kv, long kv_ld, int interleaved, void* q_out, int q_dtype, long q_ld, int n_tokens, int heads, int dim,
                           int rot, int rank,
                           const void* norm_w, int w_dtype, float eps, const float* cos_t, const float* sin_t,
                           const int* positions, const int* slots, void* cache, int has_kv, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rot % 2) return (int)cudaErrorInvalidValue;
+    const long esize = dtype == FL_F32 ? 4 : 2;
+    if (kv == nullptr) {
+        kv = (const char*)proj + (long)heads * (dim + rot) * esize;
+        kv_ld = ld;
+    }
     FL_DISPATCH(dtype, T, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(q_dtype, TQ,
-        return fl_launch(latent_prep_kernel<T, TW, TQ>, dim3(n_tokens), dim3(256), 0, stream, (const T*)proj, ld, (TQ*)q_out,
+        return fl_launch(latent_prep_kernel<T, TW, TQ>, dim3(n_tokens), dim3(256), 0, stream, (const T*)proj, ld, (const T*)kv, kv_ld, interleaved, (TQ*)q_out,
                          q_ld, heads, dim, rot, rank, (const TW*)norm_w, eps, cos_t, sin_t, positions, slots, (T*)cache,
                          has_kv))));
     return 0;

@@ -493,17 +493,23 @@ def delta_gated_norm(work, o_col, proj, gate_col, weight, out, heads, vdim, eps)
 
 # ---------------------------------------------------------- latent attention
 
-def latent_prep(proj, q_out, heads, dim, rot, rank, norm_w, eps, cos, sin, positions, slots, cache):
+def latent_prep(proj, q_out, heads, dim, rot, rank, norm_w, eps, cos, sin, positions, slots, cache, kv=None,
+                interleaved=False):
     """The queries' rotated parts, turned, go to the last `rot` columns of each head's block of `q_out`
     ([N, heads * (rank + rot)], float32 or bfloat16); with `cache` ([pages, page_size, rank + rot]), each token's latent
-    is normed and written with the rotated key part into the token's row."""
-    _require_cuda(proj, q_out, norm_w, cos, sin, positions, slots, cache)
+    is normed and written with the rotated key part into the token's row.  The latent and the key part follow the
+    queries in `proj`'s rows, or are the rows of `kv` ([N, rank + rot]).  Rotary pairs are (i, i + rot/2), with
+    `interleaved` (2i, 2i + 1)."""
+    _require_cuda(proj, q_out, norm_w, cos, sin, positions, slots, cache, kv)
+    if kv is not None and kv.dtype != proj.dtype:
+        raise KernelError("latent_prep: queries and latents must have one dtype")
     if cache is not None and (cache.dtype != proj.dtype or not cache.is_contiguous()):
         raise KernelError("latent_prep: the cache must be contiguous and of the activations' dtype")
-    fn = _fn("latent_attention", "fl_latent_prep", [c_void_p, c_int, c_long, c_void_p, c_int, c_long, c_int, c_int, c_int, c_int,
+    fn = _fn("latent_attention", "fl_latent_prep", [c_void_p, c_int, c_long, c_void_p, c_long, c_int, c_void_p, c_int, c_long, c_int, c_int, c_int, c_int,
                                                     c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
                                                     c_void_p, c_void_p, c_int, c_void_p])
-    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(q_out), dtype_code(q_out), _ld(q_out), proj.shape[0], heads,
+    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(kv), 0 if kv is None else _ld(kv), int(bool(interleaved)),
+              _ptr(q_out), dtype_code(q_out), _ld(q_out), proj.shape[0], heads,
               dim, rot, rank,
               _ptr(norm_w), F32 if norm_w is None else dtype_code(norm_w), float(eps), _ptr(cos), _ptr(sin),
               _ptr(positions), _ptr(slots), _ptr(cache), 0 if cache is None else 1, _stream()), "latent_prep")
@@ -578,6 +584,106 @@ def gemm_batched(a, a_batch, w, out, out_batch):
                   batch, _stream()), "gemm_mma_batched")
         return
     gemm_simt_batched(a, a_batch, w, out, out_batch)
+
+
+# ------------------------------------------ post-norm block with input convolution; paired-token embedding
+
+def input_conv(x, w, taps, ring, step, h, hc):
+    """hc[t] = x[t] + sum_j w[:, j] x[t - taps + 1 + j] over the request's own rows (zeros before position 0; rows of
+    earlier steps from `ring`, [slots, (taps - 1) * width] float32 filed by position mod (taps - 1)); h[t] = x[t] in the
+    activation type (None: not wanted).  x float32 [N, width], w float32 [width, taps]."""
+    _require_cuda(x, w, ring, h, hc)
+    if x.dtype != torch.float32 or w.dtype != torch.float32 or (ring is not None and ring.dtype != torch.float32):
+        raise KernelError("input_conv: the stream, the taps and the kept rows must be float32")
+    if h is not None and h.dtype != hc.dtype:
+        raise KernelError("input_conv: both outputs share a dtype")
+    fn = _fn("gated_block", "fl_input_conv", [c_void_p, c_long, c_void_p, c_int, c_void_p, c_long, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int,
+                                              c_void_p])
+    _check(fn(_ptr(x), _ld(x), _ptr(w), int(taps), _ptr(ring), 0 if ring is None else ring.stride(0), _ptr(step.positions),
+              _ptr(step.tok_req), _ptr(step.req_start), _ptr(step.req_slot), _ptr(h), 0 if h is None else _ld(h), _ptr(hc),
+              _ld(hc), dtype_code(hc), x.shape[0], x.shape[1], _stream()), "input_conv")
+
+
+def gated_norm_add(x, y, gate, gate_bias, w, eps, step, ring=None, taps=1):
+    """x += rmsnorm(y * sigmoid(gate + gate_bias)) * w (no gate: rmsnorm(y) * w).  With `ring`, the rows of x as they
+    were before the add are filed for the request's last taps - 1 rows of the step (see `input_conv`)."""
+    _require_cuda(x, y, gate, gate_bias, w, ring)
+    if x.dtype != torch.float32 or w.dtype != torch.float32 or (gate is not None and gate.dtype != y.dtype) or \
+            (gate_bias is not None and gate_bias.dtype != torch.float32):
+        raise KernelError("gated_norm_add: float32 stream, weights and bias; gate of the sublayer output's dtype")
+    fn = _fn("gated_block", "fl_gated_norm_add", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p,
+                                                  c_void_p, c_float, c_int, c_int, c_void_p, c_long, c_int, c_void_p,
+                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(x), _ld(x), _ptr(y), _ld(y), _ptr(gate), 0 if gate is None else _ld(gate), dtype_code(y),
+              _ptr(gate_bias), _ptr(w), float(eps), x.shape[0], x.shape[1], _ptr(ring),
+              0 if ring is None else ring.stride(0), int(taps), _ptr(step.positions), _ptr(step.tok_req),
+              _ptr(step.req_start), _ptr(step.req_qlen), _ptr(step.req_slot), _stream()), "gated_norm_add")
+
+
+def sigmoid_gate(a, g):
+    """a *= sigmoid(g), element by element, in float."""
+    _require_cuda(a, g)
+    if a.dtype != g.dtype or a.shape != g.shape:
+        raise KernelError("sigmoid_gate: both operands share shape and dtype")
+    fn = _fn("gated_block", "fl_sigmoid_gate", [c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(a), _ld(a), _ptr(g), _ld(g), dtype_code(a), a.shape[0], a.shape[1], _stream()), "sigmoid_gate")
+
+
+def pair_embed(table, pairs, out, step, last_token, buckets, mul_prev, mul_cur, scale):
+    """out[t] = table[id_t] * scale + pairs[(id_(t-1) * mul_prev + id_t * mul_cur) mod buckets] (row `buckets` for a
+    request's first token).  `last_token` ([slots] int32) keeps each request's last token between steps."""
+    _require_cuda(table, pairs, out, last_token)
+    fed = getattr(step, "token_feed", None)
+    if out.dtype != torch.float32 or table.dtype != pairs.dtype or last_token.dtype != torch.int32:
+        raise KernelError("pair_embed: out float32, both tables of one dtype, last_token int32")
+    fn = _fn("gated_block", "fl_pair_embed", [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p, c_long, c_int,
+                                              c_int, c_int, c_int, c_long, c_long, c_float, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(fn(_ptr(table), _ld(table), _ptr(pairs), _ld(pairs), dtype_code(table), _ptr(step.token_ids), _ptr(out), _ld(out),
+              step.token_ids.numel(), table.shape[1], table.shape[0], int(buckets), int(mul_prev), int(mul_cur),
+              float(scale), _ptr(step.tok_req), _ptr(step.req_start), _ptr(step.req_ctx), _ptr(step.req_qlen),
+              _ptr(step.req_slot), _ptr(last_token), _ptr(step.status), _ptr(fed), 0 if fed is None else fed.numel(),
+              _stream()), "pair_embed")
+
+
+# ------------------------------------------------- attention with soft cap, distance bias, kept first tokens, sink
+
+def sink_prep(proj, bias, q_w, k_w, eps, q_out, heads, kv_heads, dim, vdim, v_mode, lam, v_first, slots, cache, page_size):
+    """Biases, the whole-projection norms of q and k, the blend of v with `v_first` (v_mode 0: none, 1: v is kept in
+    v_first, 2: v <- (1 - lam) v + lam v_first); q to `q_out`, k and v into the tokens' rows of `cache`
+    ([pages, kv_heads, page_size, dim + vdim])."""
+    _require_cuda(proj, bias, q_w, k_w, q_out, v_first, slots, cache)
+    if cache.dtype != proj.dtype or not cache.is_contiguous():
+        raise KernelError("sink_prep: the cache must be contiguous and of the activations' dtype")
+    for v in (bias, q_w, k_w, v_first):
+        if v is not None and v.dtype != torch.float32:
+            raise KernelError("sink_prep: biases, norm weights and the first values are float32")
+    fn = _fn("sink_attention", "fl_sink_prep", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+                                                c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                                c_long, c_void_p, c_void_p, c_long, c_int, c_void_p])
+    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(bias), _ptr(q_w), _ptr(k_w), float(eps), _ptr(q_out),
+              dtype_code(q_out), _ld(q_out), proj.shape[0], heads, kv_heads, dim, vdim, int(v_mode), float(lam),
+              _ptr(v_first), 0 if v_first is None else _ld(v_first), _ptr(slots), _ptr(cache), cache.stride(0), page_size,
+              _stream()), "sink_prep")
+
+
+def sink_attention_simt(q, out, cache, block_table, tok_req, positions, heads, kv_heads, dim, vdim, window, keep_first,
+                        scale, cap, bucket_of, rel, sink, page_size):
+    """Attention of every token over its request's visible keys (the last `window` and the first `keep_first`), scores
+    capped (`cap` None or 0: not), biased by `rel[bucket_of[distance]]` and with `sink` in the denominator (each may be
+    None).  CUDA cores, any sizes, both number formats."""
+    _require_cuda(q, out, cache, block_table, tok_req, positions, bucket_of, rel, sink)
+    if vdim > 256:
+        raise KernelError(f"sink_attention: value size {vdim} is beyond the kernel's limit of 256")
+    fn = _fn("sink_attention", "fl_sink_attention_simt",
+             [c_void_p, c_int, c_long, c_void_p, c_long, c_void_p, c_int, c_long, c_int, c_void_p, c_int, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p, c_void_p,
+              c_void_p])
+    _check(fn(_ptr(q), dtype_code(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), dtype_code(cache), cache.stride(0), page_size,
+              _ptr(block_table), block_table.stride(0), _ptr(tok_req), _ptr(positions), q.shape[0], heads, kv_heads, dim,
+              vdim, int(window or 0), int(keep_first or 0), float(scale), float(cap or 0.0), _ptr(bucket_of),
+              0 if bucket_of is None else bucket_of.numel(), _ptr(rel), _ptr(sink), _stream()), "sink_attention_simt")
 
 
 # ------------------------------------------------------------- routed experts

@@ -1,4 +1,4 @@
-from . import attention, block, delta, differential, io, latent, mlp, moe, norm, retention, rotary  # noqa: F401  (registers the built-in parts)
+from . import attention, block, delta, differential, io, latent, mlp, moe, norm, retention, rotary, sink_attention  # noqa: F401  (registers the built-in parts)
 from .base import BuildContext, EngineLimits, Part, ResidualStream, Workspace
 from .decoder import Decoder
 from .plan import LayerRun, LayerSpec, ModelPlan, PartSpec

@@ -107,6 +107,21 @@ class ResidualStream:
         self.extra = None            # a second tensor not yet added (a layer whose mixer and feed-forward run side by
                                      # side leaves two); a norm with `takes_extra` adds both while it reads
 
+    def settle(self):
+        """x takes in whatever is still pending (for a block whose sublayers read x itself)."""
+        from ..native import ops
+        if self.pending is not None and not isinstance(self.pending, torch.Tensor):
+            self.pending = self.pending.reduce_into(self.spill())
+        if self.pending is not None:
+            if self.pending_norm is not None:
+                self.pending_norm.add_normed(self)
+            else:
+                ops.residual_add(self.x, self.pending)
+                self.pending = None
+        if self.extra is not None:
+            ops.residual_add(self.x, self.extra)
+            self.extra = None
+
     def norm_into(self, norm, out, rows=None):
         """`norm.apply(self, out, rows)`, with a pending sum that the norm can take."""
         pending = self.pending

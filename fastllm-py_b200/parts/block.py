@@ -140,3 +140,106 @@ class ParallelBlock(Part):
             if left is not None:
                 left.reduce_into(delta_ff)
             stream.extra = delta_ff
+
+
+@register_part("block", "gated_postnorm")
+class GatedPostNormBlock(Part):
+    """A layer whose sublayers read the residual stream itself and are normed on their OUTPUT only:
+        h = x;  hc = h + conv(h);  x <- x + norm_out(sublayer(hc) * sigmoid(W_gate h + b_gate))
+    for the mixer and then (if the layer has one) the feed-forward.  conv is a causal convolution over time on each
+    channel with `taps` taps (no bias; zeros before the sequence's start), whose last taps - 1 input rows per
+    sublayer are per-request state, filed by position; the gate reads h as it was before the convolution.
+    params: hidden_size, taps (0: no convolution), gate (bool).  norm roles: "mixer_out" and, with a feed-forward,
+    "ff_out".  tensors: conv_mixer, conv_ff [hidden, taps]; gate_mixer, gate_ff [hidden, hidden] with
+    gate_mixer_bias, gate_ff_bias [hidden]."""
+    category = "block"
+    native_libraries = ("gated_block",)
+
+    def __init__(self, layer_spec, ctx):
+        super().__init__(layer_spec, ctx)
+        p = layer_spec.params
+        self.hidden = int(p["hidden_size"])
+        self.taps = int(p.get("taps") or 0)
+        self.gated = bool(p.get("gate", True))
+        self.mixer = build_part("mixer", layer_spec.mixer, ctx)
+        self.norm_mixer_out = build_part("norm", layer_spec.norms["mixer_out"], ctx)
+        self.feed_forward = self.norm_ff_out = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, ctx)
+            self.norm_ff_out = build_part("norm", layer_spec.norms["ff_out"], ctx)
+        self.subs = ["mixer"] + (["ff"] if self.feed_forward is not None else [])
+        self.conv, self.gate, self.gate_bias, self._w_out = {}, {}, {}, {}
+
+    def children(self):
+        parts = [self.mixer, self.norm_mixer_out]
+        if self.feed_forward is not None:
+            parts += [self.feed_forward, self.norm_ff_out]
+        return parts
+
+    def weight_shapes(self):
+        shapes = {}
+        for s in self.subs:
+            if self.taps:
+                shapes[f"conv_{s}"] = (self.hidden, self.taps)
+            if self.gated:
+                shapes[f"gate_{s}"] = (self.hidden, self.hidden)
+                shapes[f"gate_{s}_bias"] = (self.hidden,)
+        return shapes
+
+    def load(self, tensors):
+        from .linear import Linear
+        for s in self.subs:
+            if self.taps:
+                self.conv[s] = tensors[f"conv_{s}"].float().contiguous()
+            else:                                             # one tap of weight zero: hc = h
+                self.conv[s] = torch.zeros((self.hidden, 1), dtype=torch.float32, device=self.ctx.device)
+            if self.gated:
+                self.gate[s] = Linear([tensors[f"gate_{s}"]])
+                self.gate_bias[s] = tensors[f"gate_{s}_bias"].float().contiguous()
+
+    def state_need(self):
+        from ..cache.needs import FixedState
+        back = self.taps - 1
+        return FixedState((len(self.subs) * back * self.hidden,), "float32") if back > 0 else None
+
+    def reserve(self, limits):
+        for lin in self.gate.values():
+            lin.reserve(self.ctx.dtype, limits.max_tokens)
+
+    def _out_weight(self, s, norm):
+        w = self._w_out.get(s)
+        if w is None:
+            w = self._w_out[s] = norm.weight.float().contiguous()
+        return w
+
+    def _sublayer(self, s, index, norm, run, stream, step, state):
+        from ..native import ops
+        n = stream.x.shape[0]
+        dt = self.ctx.dtype
+        ws = step.workspace
+        taps = max(self.taps, 1)
+        ring = None
+        if taps > 1:
+            span = (taps - 1) * self.hidden
+            ring = state.tensor[:, index * span:(index + 1) * span]
+        h = ws.rows("normed", n, self.hidden, dt) if self.gated else None
+        hc = ws.rows("conv_in", n, self.hidden, dt)
+        ops.input_conv(stream.x, self.conv[s], taps, ring, step, h, hc)
+        delta = ws.rows("delta", n, self.hidden, dt)
+        left = run(hc, delta)
+        if left is not None:
+            left.reduce_into(delta)
+        gate = None
+        if self.gated:
+            gate = ws.rows("branch_gate", n, self.hidden, dt)
+            self.gate[s].forward(h, gate)
+        ops.gated_norm_add(stream.x, delta, gate, self.gate_bias.get(s), self._out_weight(s, norm), norm.eps, step,
+                           ring, taps)
+
+    def forward(self, stream, step, cache, state=None):
+        stream.settle()                                       # the sublayers read x itself
+        self._sublayer("mixer", 0, self.norm_mixer_out, lambda hc, out: self.mixer.forward(hc, out, step, cache),
+                       stream, step, state)
+        if self.feed_forward is not None:
+            self._sublayer("ff", 1, self.norm_ff_out, lambda hc, out: self.feed_forward.forward(hc, out, step),
+                           stream, step, state)

@@ -94,14 +94,26 @@ class Decoder:
             part.shared_slots = frozenset(slot for slot in shapes if users[tensors[slot]] > 1)
             part.load({slot: tensors_by_name[tensors[slot]] for slot in shapes})
 
+    EMBEDDING_STATE = "embedding"        # cache id of the embedding part's per-request state
+
     def cache_needs(self) -> dict:
-        """run index -> need, for the runs that own a cache or a state."""
+        """cache id -> need: the run index for the runs whose mixer owns a cache or a state; ("block", run index)
+        for a block arrangement with per-request state of its own (`state_need()`); `EMBEDDING_STATE` for an
+        embedding part with one."""
         needs = {}
         for i, run in enumerate(self.order):
             if run.cache is None:
                 need = self.blocks[run.layer].mixer.cache_need()
                 if need is not None:
                     needs[i] = need
+            fn = getattr(self.blocks[run.layer], "state_need", None)
+            need = fn() if fn is not None else None
+            if need is not None:
+                needs[("block", i)] = need
+        fn = getattr(self.embedding, "state_need", None)
+        need = fn() if fn is not None else None
+        if need is not None:
+            needs[self.EMBEDDING_STATE] = need
         return needs
 
     @property
@@ -164,10 +176,18 @@ class Decoder:
         ws = step.workspace
         stream = ResidualStream(ws.rows("residual", n, self.hidden, torch.float32),
                                 spill=lambda: ws.rows("delta", n, self.hidden, self.ctx.dtype))
-        self.embedding.forward(step, stream.x)
+        if hasattr(self.embedding, "state_need"):
+            self.embedding.forward(step, stream.x, step.cache_view(self.EMBEDDING_STATE, True))
+        else:
+            self.embedding.forward(step, stream.x)
         for i, run in enumerate(self.order):
             cache_id = i if run.cache is None else run.cache
-            self.blocks[run.layer].forward(stream, step, step.cache_view(cache_id, run.cache is None))
+            block = self.blocks[run.layer]
+            cache = step.cache_view(cache_id, run.cache is None)
+            if hasattr(block, "state_need"):
+                block.forward(stream, step, cache, step.cache_view(("block", i), True))
+            else:
+                block.forward(stream, step, cache)
         m = step.n_wanted
         logits = ws.rows("logits", m, self.vocab, torch.float32, initial=64)
         if m > 0:

@@ -36,6 +36,42 @@ class Embedding(Part):
         ops.embed(self.table, step.token_ids, out, step.status, getattr(step, "token_feed", None), self.scale)
 
 
+@register_part("embedding", "table_pairs")
+class PairEmbedding(Embedding):
+    """x = table[id] * scale + pairs[(previous id * mul_prev + id * mul_cur) mod buckets]: a second, hashed table
+    indexed by the token and the one before it; a sequence's first token takes the table's last row (`buckets`).
+    The token before a step's first one is per-request state (one int32 per request slot).
+    params: vocab_size, hidden_size, scale, buckets, mul_prev, mul_cur.  tensors: weight [vocab, hidden],
+    pairs [buckets + 1, hidden]."""
+    native_libraries = ("gated_block",)
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        self.buckets = int(spec.params["buckets"])
+        self.mul_prev = int(spec.params["mul_prev"])
+        self.mul_cur = int(spec.params["mul_cur"])
+        if self.buckets < 1:
+            raise ValueError("table_pairs: buckets must be at least 1")
+        self.pairs = None
+
+    def weight_shapes(self):
+        return {"weight": (self.vocab, self.hidden), "pairs": (self.buckets + 1, self.hidden)}
+
+    def state_need(self):
+        from ..cache.needs import FixedState
+        return FixedState((1,), "int32")
+
+    def load(self, tensors):
+        self.table = tensors["weight"]
+        self.pairs = tensors["pairs"]
+        if self.pairs.dtype != self.table.dtype:
+            raise ValueError("table_pairs: both tables must be stored in one dtype")
+
+    def forward(self, step, out, state):
+        ops.pair_embed(self.table, self.pairs, out, step, state.tensor, self.buckets, self.mul_prev, self.mul_cur,
+                       self.scale)
+
+
 @register_part("head", "linear")
 class LinearHead(Part):
     """params: vocab_size, hidden_size, softcap (None | c > 0).  tensors: weight [vocab, hidden]."""

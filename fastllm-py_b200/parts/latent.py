@@ -20,6 +20,13 @@ that are multiples of 32, they and the attention itself run on the tensor cores
 A layer with `shares_cache` has no W_dkv: it reads the rows another layer's run
 wrote, with its own queries, W_uk, W_uv, window and scale.  The cache keeps what
 the widest window among the layers that read it needs (`keep`).
+
+Two variants by parameter.  `q_rank`: the queries go through a latent of their
+own, c_q = RMSnorm(W_dq h) * w, q = W_uq c_q, instead of one matrix W_q; W_dq
+is then stacked with W_dkv (and the gate) into the layer's first product.
+`out_gate`: the concatenated heads are multiplied by sigmoid(W_g h) before W_o.
+`pairing` names the rotary pairs: "halves" (i, i + rot_dim/2) or "interleaved"
+(2i, 2i + 1); pair i turns by the position table's column i either way.
 """
 from __future__ import annotations
 
@@ -35,11 +42,14 @@ from .registry import build_part, register_part
 @register_part("mixer", "latent_attention")
 class LatentAttention(Part):
     """params: hidden_size, heads, dim, rot_dim, vdim, kv_rank, scale, window (None | int), keep (None | int: what the
-    cache keeps; absent: `window`), norm_eps, position (PartSpec of rot_dim dims), shares_cache (bool).
-    tensors: q [heads * (dim + rot_dim), hidden], uk [heads * dim, kv_rank], uv [heads * vdim, kv_rank],
-    o [hidden, heads * vdim] and, unless shares_cache, dkv [kv_rank + rot_dim, hidden], dkv_norm [kv_rank]."""
+    cache keeps; absent: `window`), norm_eps, position (PartSpec of rot_dim dims), shares_cache (bool),
+    q_rank (None | int), out_gate (bool), pairing ("halves" | "interleaved").
+    tensors: q [heads * (dim + rot_dim), hidden] (with q_rank instead: dq [q_rank, hidden], dq_norm [q_rank],
+    uq [heads * (dim + rot_dim), q_rank]), uk [heads * dim, kv_rank], uv [heads * vdim, kv_rank],
+    o [hidden, heads * vdim], with out_gate g [heads * vdim, hidden], and, unless shares_cache,
+    dkv [kv_rank + rot_dim, hidden], dkv_norm [kv_rank]."""
     category = "mixer"
-    native_libraries = ("latent_attention", "gemm_mma")
+    native_libraries = ("latent_attention", "gemm_mma", "gated_block")
     SPLIT_BELOW = 64                 # blocks (tokens x groups of 16 heads) under which a step's keys are split
     SCRATCH = "latent attention splits"
 
@@ -54,6 +64,11 @@ class LatentAttention(Part):
         self.keep = p["keep"] if "keep" in p else self.window
         self.norm_eps = float(p["norm_eps"])
         self.shares_cache = bool(p.get("shares_cache", False))
+        self.q_rank = int(p["q_rank"]) if p.get("q_rank") else None
+        self.out_gate = bool(p.get("out_gate", False))
+        if p.get("pairing", "halves") not in ("halves", "interleaved"):
+            raise ValueError(f"latent_attention: pairing {p.get('pairing')!r} is neither 'halves' nor 'interleaved'")
+        self.interleaved = p.get("pairing", "halves") == "interleaved"
         if self.rank > 1024:
             raise ValueError(f"latent_attention: kv_rank {self.rank} is beyond the kernel's limit of 1024")
         if self.window is not None and self.keep is not None and self.keep < self.window:
@@ -63,7 +78,7 @@ class LatentAttention(Part):
             raise ValueError("latent_attention: the position encoding must turn exactly rot_dim dimensions")
         self.q_cols = self.heads * (self.dim + self.rot)
         self.width = self.rank + self.rot                               # a cache row
-        self.proj = self.o = None
+        self.proj = self.o = self.uq = self.dq_norm = None
 
     def children(self):
         return [self.position]
@@ -72,25 +87,40 @@ class LatentAttention(Part):
         return None if self.shares_cache else PagedRows(self.width, self.keep)
 
     def weight_shapes(self):
-        shapes = {"q": (self.q_cols, self.hidden), "uk": (self.heads * self.dim, self.rank),
+        shapes = {"uk": (self.heads * self.dim, self.rank),
                   "uv": (self.heads * self.vdim, self.rank), "o": (self.hidden, self.heads * self.vdim)}
+        if self.q_rank is None:
+            shapes["q"] = (self.q_cols, self.hidden)
+        else:
+            shapes.update({"dq": (self.q_rank, self.hidden), "dq_norm": (self.q_rank,),
+                           "uq": (self.q_cols, self.q_rank)})
+        if self.out_gate:
+            shapes["g"] = (self.heads * self.vdim, self.hidden)
         if not self.shares_cache:
             shapes["dkv"] = (self.width, self.hidden)
             shapes["dkv_norm"] = (self.rank,)
         return shapes
 
     def load(self, tensors):
-        mats = [tensors["q"]] if self.shares_cache else [tensors["q"], tensors["dkv"]]
+        # the layer's first product: [q or dq | dkv | g], everything that reads h
+        mats = [tensors["q"] if self.q_rank is None else tensors["dq"]]
+        if not self.shares_cache:
+            mats.append(tensors["dkv"])
+        if self.out_gate:
+            mats.append(tensors["g"])
         if len({m.dtype for m in mats}) != 1:
-            raise ValueError("latent_attention: q and dkv matrices must be stored in one dtype")
+            raise ValueError("latent_attention: the matrices that read the layer's input must be stored in one dtype")
         self.proj = Linear(mats)
+        if self.q_rank is not None:
+            self.uq = Linear([tensors["uq"]])
+            self.dq_norm = tensors["dq_norm"].contiguous()
         self.dkv_norm = None if self.shares_cache else tensors["dkv_norm"].contiguous()
         self.uk_t = tensors["uk"].view(self.heads, self.dim, self.rank).transpose(1, 2).contiguous()
         self.uv = tensors["uv"].view(self.heads, self.vdim, self.rank).contiguous()
         self.o = Linear([tensors["o"]])
 
     def reserve(self, limits):
-        for lin in (self.proj, self.o):
+        for lin in (self.proj, self.o, self.uq):
             if lin is not None:
                 lin.reserve(self.ctx.dtype, limits.max_tokens)
         if self.ctx.device.type == "cuda" and ops.latent_tc_takes(self.ctx.dtype, self.rank, self.rot):
@@ -132,14 +162,27 @@ class LatentAttention(Part):
         ws = step.workspace
         if cache.writes == self.shares_cache:
             raise RuntimeError("latent_attention: the run's cache and the layer's shares_cache disagree")
-        cols = self.q_cols if self.shares_cache else self.q_cols + self.width
+        first = self.q_cols if self.q_rank is None else self.q_rank
+        kv_cols = 0 if self.shares_cache else self.width
+        cols = first + kv_cols + (self.heads * self.vdim if self.out_gate else 0)
         proj = ws.rows("latent_proj", n, cols, dt)
         self.proj.forward(h, proj)
+        kv = None
+        if self.q_rank is not None or self.out_gate:          # the latent's rows do not directly follow the queries
+            kv = None if self.shares_cache else proj[:, first:first + kv_cols]
+        queries = proj
+        if self.q_rank is not None:
+            cq = ws.rows("latent_cq", n, self.q_rank, dt)
+            ops.rmsnorm(proj[:, :self.q_rank], self.dq_norm, cq, self.norm_eps)
+            queries = ws.rows("latent_queries", n, self.q_cols, dt)
+            self.uq.forward(cq, queries)
         tc = ops.latent_tc_takes(dt, self.rank, self.rot)     # bfloat16 and sizes the tensor-core kernel is built for
         q = ws.rows("latent_q", n, self.heads * self.width, dt if tc else torch.float32)
         cos, sin = self.position.tables()
-        ops.latent_prep(proj, q, self.heads, self.dim, self.rot, self.rank, self.dkv_norm, self.norm_eps, cos, sin,
-                        step.positions, cache.slots, cache.tensor if cache.writes else None)
+        ops.latent_prep(queries, q, self.heads, self.dim, self.rot, self.rank, self.dkv_norm, self.norm_eps, cos, sin,
+                        step.positions, cache.slots, cache.tensor if cache.writes else None, kv=kv,
+                        interleaved=self.interleaved)
+        proj = queries
         ops.gemm_batched(proj, self.dim + self.rot, self.uk_t, q, self.width)
         mix = ws.rows("latent_mix", n, self.heads * self.rank, dt if tc else torch.float32)
         if tc:
@@ -154,4 +197,6 @@ class LatentAttention(Part):
                                  self.rank, self.rot, self.window, self.scale, cache.page_size)
         ctx = ws.rows("latent_ctx", n, self.heads * self.vdim, dt)
         ops.gemm_batched(mix, self.rank, self.uv, ctx, self.vdim)
+        if self.out_gate:
+            ops.sigmoid_gate(ctx, ws.rows("latent_proj", n, cols, dt)[:, first + kv_cols:])
         return self.o.forward(ctx, out, defer=True)

@@ -78,3 +78,24 @@ class RMSNorm(Part):
         mean square, so one pass serves both.  The pending sum must be a tensor (or none) without a norm of its own."""
         ops.norm_pair(stream.x, stream.pending, stream.extra, self.weight, other.weight, out, out_other, self.eps)
         stream.pending = stream.extra = None
+
+
+@register_part("norm", "rmsnorm_scalar")
+class ScalarRMSNorm(RMSNorm):
+    """RMSNorm whose weight is ONE stored number g for all coordinates: x * (mean(x^2) + eps)^-1/2 * g.
+    With a `scale` tensor (one factor per coordinate applied to the normed row, a layer scale) the two are one
+    vector, g * scale, formed in float32 at load; every kernel of RMSNorm then serves.
+    params: size, eps.  tensors: weight [] and, optionally, scale [size]."""
+
+    def weight_shapes(self):
+        shapes = {"weight": ()}
+        if "scale" in self.spec.tensors:
+            shapes["scale"] = (self.size,)
+        return shapes
+
+    def load(self, tensors):
+        g = tensors["weight"].float().reshape(1)
+        if "scale" in tensors:
+            self.weight = (g * tensors["scale"].float()).contiguous()
+        else:
+            self.weight = g.expand(self.size).contiguous()

@@ -28,11 +28,14 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """A layer = an arrangement (`block`) of a mixer, a feed-forward and norms."""
+    """A layer = an arrangement (`block`) of a mixer, a feed-forward and norms.  An arrangement with sizes,
+    constants or tensors of its own (a gate on the residual branch, say) has them in `params` and `tensors`."""
     block: str
     mixer: PartSpec
     feed_forward: PartSpec | None      # None: the layer is a mixer only (blocks that allow it)
     norms: dict            # role in the block -> PartSpec
+    params: dict = field(default_factory=dict)
+    tensors: dict = field(default_factory=dict)     # the block's own slots -> tensor names in the checkpoint
 
 
 @dataclass(frozen=True)
@@ -88,6 +91,10 @@ class ModelPlan:
 
         visit(self.embedding)
         for layer in self.layers:
+            for name in layer.tensors.values():
+                if name not in seen:
+                    seen.add(name)
+                    names.append(name)
             visit(layer.mixer)
             if layer.feed_forward is not None:
                 visit(layer.feed_forward)

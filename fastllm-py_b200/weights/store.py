@@ -78,7 +78,7 @@ class RandomStore:
 
     Each tensor has a generator of its own, keyed by (seed, name), so a tensor's
     values do not depend on which others exist or in which order they are made.
-    Matrices and tables are N(0, std); vectors (norm weights) are 1 + N(0, norm_std).
+    Matrices and tables are N(0, std); vectors and single numbers (norm weights) are 1 + N(0, norm_std).
     Values are drawn in float32 on the CPU and rounded to `dtype`; `on_device`
     draws on the device instead (other values, for models too large to stage)."""
 
@@ -106,7 +106,7 @@ class RandomStore:
         gen_device = device if self.on_device else "cpu"
         gen = torch.Generator(device=gen_device)
         gen.manual_seed(self._seed_for(name))
-        if len(shape) == 1:
+        if len(shape) <= 1:
             t = torch.empty(shape, dtype=torch.float32, device=gen_device).normal_(
                 0.0, self.norm_std, generator=gen).add_(1.0)
         elif self.on_device:

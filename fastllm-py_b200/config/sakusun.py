@@ -166,8 +166,8 @@ class SakusunConfig:
             layers.append(SakusunLayerConfig(lr["type"], _mixer(lr["type"], _sub(lr, "mixer", f"layers[{i}]"), i),
                                              _mlp(lr.get("mlp"), i)))
         blenders = [layer.mixer for layer in layers if getattr(layer.mixer, "v_mix", False)]
-        if len({(m.kv_heads, m.vdim) for m in blenders}) > 1:
-            raise ConfigError("config.json: layers with v_mix must agree in kv_heads and vdim (they blend their values)")
+        if len({m.kv_heads * m.vdim for m in blenders}) > 1:
+            raise ConfigError("config.json: layers with v_mix must agree in kv_heads * vdim (they blend their values)")
         norm = KeyReader(_sub(raw, "norm", "config"))
         emb = r.mapping("embedding") or {}
         bigram = KeyReader(emb).mapping("bigram")

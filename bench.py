@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--workload decode|serve|67b|tables|hybrid|lasonex]
+                    [--workload decode|serve|67b|tables|hybrid|lasonex|sakusun]
 
 The default run is the DeepSeek-LLM-7B sized model (30 layers, hidden 4096,
 32 heads, head size 128, feed-forward 11008, vocabulary 102400) with random
@@ -44,6 +44,8 @@ Two more workloads, each printing one line of its own:
                      beside the dense decoder of equal width and depth: prompt and decode steps
   --workload lasonex the Lasonex design (differential attention + retention in parallel layers, grouped experts)
                      at the same two widths, beside the Tigitar hybrid and the dense decoder
+  --workload sakusun the Sakusun design (windowed sink attention + latent attention in gated post-norm layers with an
+                     input convolution) at the same two widths, beside the Tigitar hybrid and the dense decoder
   --workload 67b     deepseek-llm-67b size (95 layers, hidden 8192, 64 heads over 8 key/value
              heads; 135 GB of weights on the one GPU): a 2048-token prompt step and decode
              steps at batch 1, 8 and 16 with 4000-token contexts, with their roofline fractions.
@@ -799,6 +801,145 @@ def run_lasonex(args, warmup):
     return 0
 
 
+SAKUSUN_SIZES = {
+    # gated post-norm layers at the widths of HYBRID_SIZES: three latent-attention layers (queries through a latent of
+    # their own, an output gate) to one windowed sink-attention layer, a dense gelu unit in every layer; the dense
+    # Llama-style decoder of the same width, depth and feed-forward size is timed beside it
+    "w2048": dict(width=2048, vocab=32256, layers=8, ff=5504, taps=3, buckets=100003,
+                  attention=dict(heads=16, kv_heads=4, dim=128, vdim=128, window=1024, keep_first=64, bias_max=2048.0),
+                  latent=dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=768)),
+    "w4096": dict(width=4096, vocab=32256, layers=4, ff=11008, taps=3, buckets=100003,
+                  attention=dict(heads=32, kv_heads=8, dim=128, vdim=128, window=2048, keep_first=64, bias_max=4096.0),
+                  latent=dict(heads=32, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1536)),
+}
+
+
+def sakusun_config(size):
+    """A Sakusun configuration of `size`: layers cycle through latent attention, sink attention (blending its values
+    with the first such layer's), latent attention, latent attention; a dense gelu unit in every layer."""
+    from fastllm_py_b200.config.sakusun import (DenseConfig, QueryLatentAttentionConfig, SakusunConfig,
+                                                SakusunLayerConfig, SinkAttentionConfig)
+
+    z = SAKUSUN_SIZES[size]
+    a, m = z["attention"], z["latent"]
+    attention = SinkAttentionConfig(a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["dim"] ** -0.5, 50.0, a["bias_max"],
+                                    a["window"], a["keep_first"], True)
+    latent = QueryLatentAttentionConfig(m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"],
+                                        (m["dim"] + m["rot_dim"]) ** -0.5, 10000.0)
+    layers = [SakusunLayerConfig("attention", attention, DenseConfig(z["ff"])) if i % 4 == 1 else
+              SakusunLayerConfig("latent_attention", latent, DenseConfig(z["ff"])) for i in range(z["layers"])]
+    return SakusunConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, embedding_scale=1.0,
+                         bigram_buckets=z["buckets"], bigram_mul_prev=31, bigram_mul_cur=7, taps=z["taps"],
+                         layers=tuple(layers))
+
+
+def sakusun_decode_bytes(cfg, batch, context):
+    """Bytes a decode step has to move: the weights it uses once in bfloat16 (the gate matrices of the residual
+    branches among them), the cache rows inside each window plus the kept first tokens, the latent rows of the whole
+    context, and every request's kept convolution rows read and written in float."""
+    from fastllm_py_b200.config.sakusun import SinkAttentionConfig
+
+    w, total = cfg.width, 0
+    for layer in cfg.layers:
+        m = layer.mixer
+        subs = 1 if layer.mlp is None else 2
+        total += subs * (2 * w * w + batch * 2 * 4 * max(cfg.taps - 1, 0) * w)
+        if isinstance(m, SinkAttentionConfig):
+            total += 2 * w * (m.heads * m.dim + m.kv_heads * (m.dim + m.vdim) + m.heads * m.vdim)
+            seen = min(context, (m.window + m.keep_first) if m.window else context)
+            total += batch * seen * m.kv_heads * (m.dim + m.vdim) * 2
+        else:
+            total += 2 * (w * (m.q_rank + m.kv_rank + m.rot_dim + m.heads * m.vdim) + m.q_rank * m.heads * (m.dim + m.rot_dim)
+                          + m.heads * m.kv_rank * (m.dim + m.vdim) + m.heads * m.vdim * w)
+            total += batch * context * (m.kv_rank + m.rot_dim) * 2
+        if layer.mlp is not None:
+            total += 2 * 3 * w * layer.mlp.ff
+    return total + 2 * w * cfg.vocab + 2 * batch * w
+
+
+def sakusun_prefill_flops(cfg, tokens):
+    """Matrix-product FLOPs of a prompt step: projections, residual gates, feed-forwards, sink attention over the
+    window and the kept tokens, latent attention in latent space over every earlier token, head."""
+    from fastllm_py_b200.config.sakusun import SinkAttentionConfig
+
+    w, total = cfg.width, 0
+    for layer in cfg.layers:
+        m = layer.mixer
+        subs = 1 if layer.mlp is None else 2
+        total += subs * 2 * tokens * w * w
+        if isinstance(m, SinkAttentionConfig):
+            total += 2 * tokens * w * (m.heads * m.dim + m.kv_heads * (m.dim + m.vdim) + m.heads * m.vdim)
+            seen = sum(min(p + 1, (m.window + m.keep_first) if m.window else p + 1) for p in range(tokens))
+            total += 2 * m.heads * seen * (m.dim + m.vdim)
+        else:
+            total += 2 * tokens * (w * (m.q_rank + m.kv_rank + m.rot_dim + m.heads * m.vdim)
+                                   + m.q_rank * m.heads * (m.dim + m.rot_dim) + m.heads * m.kv_rank * (m.dim + m.vdim)
+                                   + m.heads * m.vdim * w)
+            seen = sum(p + 1 for p in range(tokens))
+            total += 2 * m.heads * seen * (2 * m.kv_rank + m.rot_dim)
+        if layer.mlp is not None:
+            total += 2 * tokens * 3 * w * layer.mlp.ff
+    return total + 2 * w * cfg.vocab
+
+
+def run_sakusun(args, warmup):
+    """The Sakusun design beside the Tigitar hybrid (the model that shares its latent attention) and the dense decoder
+    of equal width, depth and feed-forward size, one JSON line: prompt steps of 512 and 2048 tokens and decode steps at
+    batch 1 and 8 over 2048-token contexts, with each model's fraction of its own roofline (measured tensor peak for
+    prompts, measured copy bandwidth for decode steps)."""
+    from fastllm_py_b200 import LlamaConfig, Model
+
+    pk = peaks()
+    steps = max(8, min(args.steps, 32))
+    out = {}
+    sampler = ClockSampler().start()
+    sampler.__enter__()
+    for size in (args.size.split(",") if args.size else list(SAKUSUN_SIZES)):
+        z, hz = SAKUSUN_SIZES[size], HYBRID_SIZES[size]
+        llama = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=None, tie_word_embeddings=False,
+                            num_layers=z["layers"], hidden_size=z["width"], vocab_size=z["vocab"], rope_theta=10000.0,
+                            rms_norm_eps=1e-6, max_position_embeddings=4096, **hz["llama"])
+        models = [("sakusun", sakusun_config(size), sakusun_prefill_flops, sakusun_decode_bytes),
+                  ("hybrid", hybrid_config(size), hybrid_prefill_flops, hybrid_decode_bytes),
+                  ("dense", llama, prefill_flops, decode_bytes)]
+        res = {}
+        for name, cfg, flops_of, bytes_of in models:
+            if args.only and name not in args.only.split(","):
+                continue
+            model = Model.from_config(cfg, seed=0, dtype="bfloat16", page_size=16, max_tokens=8 * (CONTEXT + 256),
+                                      max_requests=8, max_batched_tokens=2048, max_model_len=4096,
+                                      cuda_graph=not args.no_graph)
+            r = {"prompt_step": {}, "decode": {}}
+            for t in (512, 2048):
+                ms, _ = time_prefill(model, t, 8, 3)
+                r["prompt_step"][str(t)] = {"ms": round(ms, 3), "value": round(t * 1000.0 / ms, 1),
+                                            "frac": round(flops_of(cfg, t) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+            for b in (1, 8):
+                v, ms, launches, _ = time_decode(model, b, steps, warmup, CONTEXT)
+                ctx = CONTEXT + warmup + (steps + 1) / 2
+                r["decode"][f"{b}x{CONTEXT}"] = {"ms_per_step": round(ms, 3), "value": round(v, 1),
+                                                 "launches_per_step": launches // steps,
+                                                 "frac": round(bytes_of(cfg, b, ctx) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+            res[name] = r
+            del model
+            import gc
+
+            import torch
+            gc.collect()
+            torch.cuda.empty_cache()
+        out[size] = res
+    sampler.__exit__()
+    print(json.dumps({
+        "metric": "prompt and decode steps of the Sakusun design beside the Tigitar hybrid and the dense decoder "
+                  "of equal size, bf16",
+        "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "steps": steps, "warmup": warmup,
+        "config": {"sizes": {k: dict(SAKUSUN_SIZES[k]) for k in out}, "page_size": 16,
+                   "peaks": pk["source"], "hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"],
+                   "cuda_graph": not args.no_graph},
+        "sizes": out, "clocks": sampler.summary()}))
+    return 0
+
+
 def reference_cpu_path(ref_root, layers=1, context=256, decode_tokens=8):
     """fastllm-py's own NumPy model code (its CPU device, float32) timed at DeepSeek-LLM-7B layer
     sizes: `layers` of the 30 layers, one sequence (that path has no batch), a `context`-token
@@ -935,11 +1076,11 @@ def main():
                     help="run fewer layers of the same sizes (the line names both numbers)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "67b", "tables", "hybrid", "lasonex"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "67b", "tables", "hybrid", "lasonex", "sakusun"],
                     help="decode: the headline line (DeepSeek-LLM-7B size); serve: continuous batching at "
                          "deepseek-coder-1.3b size; 67b: prompt and decode steps at deepseek-llm-67b size")
-    ap.add_argument("--size", default="", help="hybrid, lasonex: which sizes (w2048,w4096; default both)")
-    ap.add_argument("--only", default="", help="lasonex: which of the models timed side by side (lasonex,hybrid,dense)")
+    ap.add_argument("--size", default="", help="hybrid, lasonex, sakusun: which sizes (w2048,w4096; default both)")
+    ap.add_argument("--only", default="", help="lasonex, sakusun: which of the models timed side by side (lasonex or sakusun, hybrid, dense)")
     ap.add_argument("--requests", type=int, default=128, help="serve: how many requests")
     ap.add_argument("--rate", type=float, default=16.0, help="serve: mean arrivals a second")
     ap.add_argument("--reference-cpu", action="store_true",
@@ -960,6 +1101,8 @@ def main():
         return run_tables(args, warmup)
     if args.workload == "lasonex":
         return run_lasonex(args, warmup)
+    if args.workload == "sakusun":
+        return run_sakusun(args, warmup)
     if args.workload == "hybrid":
         return run_hybrid(args, warmup)
     args.layers = args.layers or MODEL_7B["num_layers"]

@@ -69,7 +69,9 @@ class Model:
         from .native.libraries import libraries_for
         head_dims = [p.head_dim for p in decoder.all_parts() if hasattr(p, "head_dim")]
         named = [lib for p in decoder.all_parts() for lib in getattr(p, "native_libraries", ())]
-        native_build.compile_many(libraries_for(engine_config.dtype, head_dims, named))
+        # builds that a part wants for its own sizes (a kernel compiled per head size, say) join the same parallel build
+        sized = [b for p in decoder.all_parts() if hasattr(p, "native_builds") for b in p.native_builds()]
+        native_build.compile_many(libraries_for(engine_config.dtype, head_dims, named) + sized)
         expected = decoder.expected_tensors()
         if isinstance(store, _RandomSpec):
             store = RandomStore(expected, store.seed, store.std, store.norm_std,

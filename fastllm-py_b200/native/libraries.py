@@ -8,18 +8,21 @@ PART_LIBRARIES = ["rope_kv", "attention_simt", "delta_rule", "latent_attention",
 DEFAULT_HEAD_DIMS = (128,)
 
 
-def all_libraries(head_dims=DEFAULT_HEAD_DIMS, latent_sizes=((512, 64),), diff_sizes=((64, 128),)) -> list:
+def all_libraries(head_dims=DEFAULT_HEAD_DIMS, latent_sizes=((512, 64),), diff_sizes=((64, 128),),
+                  sink_sizes=((128, 128),)) -> list:
     """Every source; the attention kernels for `head_dims`, the tensor-core latent attention for
-    `latent_sizes` ((latent size, rotated key size) pairs) and the tensor-core differential attention for
-    `diff_sizes` ((map size, value size) pairs), which are compiled per size."""
+    `latent_sizes` ((latent size, rotated key size) pairs), the tensor-core differential attention for
+    `diff_sizes` ((map size, value size) pairs) and the tensor-core sink attention for `sink_sizes`
+    ((key size, value size) pairs), which are compiled per size."""
     from .attention import libraries as attention_libraries
-    from .ops import diff_tc_library, latent_tc_library
+    from .ops import diff_tc_library, latent_tc_library, sink_tc_library
 
     libs = [(name, {}) for name in BASE_LIBRARIES + PART_LIBRARIES + BF16_LIBRARIES]
     for d in head_dims:
         libs += attention_libraries(d)
     libs += [latent_tc_library(rank, rot) for rank, rot in latent_sizes]
     libs += [diff_tc_library(dim, vdim) for dim, vdim in diff_sizes]
+    libs += [sink_tc_library(dim, vdim) for dim, vdim in sink_sizes]
     return libs
 
 

@@ -686,6 +686,33 @@ def sink_attention_simt(q, out, cache, block_table, tok_req, positions, heads, k
               0 if bucket_of is None else bucket_of.numel(), _ptr(rel), _ptr(sink), _stream()), "sink_attention_simt")
 
 
+def sink_tc_takes(dtype, dim: int, vdim: int) -> bool:
+    """Whether the tensor-core sink attention serves this number format and these sizes."""
+    return dtype == torch.bfloat16 and dim % 16 == 0 and vdim % 16 == 0 and 16 <= dim <= 128 and 16 <= vdim <= 128
+
+
+def sink_tc_library(dim: int, vdim: int):
+    return "sink_attention_tc", {"SINK_DIM": dim, "SINK_VDIM": vdim}
+
+
+def sink_attention_tc(q, out, cache, block_table, step, heads, kv_heads, dim, vdim, window, keep_first, scale, cap,
+                      bucket_of, rel, sink, page_size):
+    """`sink_attention_simt` on tensor cores: q, cache and out bfloat16; one build per (dim, vdim); 64 rows of a
+    request and one head per block, single tokens as tiles of one row."""
+    _require_cuda(q, out, cache, block_table, bucket_of, rel, sink)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("sink_attention_tc: q, cache and out must be bfloat16")
+    name, defines = sink_tc_library(dim, vdim)
+    fn = _fn(name, "fl_sink_attention_tc", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_int,
+                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                            c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p], defines)
+    _check(fn(_ptr(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), cache.stride(0), page_size, _ptr(block_table),
+              block_table.stride(0), _ptr(step.req_start), _ptr(step.req_ctx), _ptr(step.req_qlen), step.n_requests,
+              q.shape[0], heads, kv_heads, int(window or 0), int(keep_first or 0), float(scale), float(cap or 0.0),
+              _ptr(bucket_of), 0 if bucket_of is None else bucket_of.numel(), _ptr(rel), _ptr(sink), _stream()),
+           "sink_attention_tc")
+
+
 # ------------------------------------------------------------- routed experts
 
 def moe_pick(logits, bias, chosen, weights, top, softmax_scores=False, renormalise=False, groups=None, keep=None,

@@ -119,6 +119,12 @@ class LatentAttention(Part):
         self.uv = tensors["uv"].view(self.heads, self.vdim, self.rank).contiguous()
         self.o = Linear([tensors["o"]])
 
+    def native_builds(self):
+        """(library, defines) pairs compiled for this part's sizes, so that a model's first load builds them beside
+        its other libraries."""
+        takes = self.ctx.device.type == "cuda" and ops.latent_tc_takes(self.ctx.dtype, self.rank, self.rot)
+        return [ops.latent_tc_library(self.rank, self.rot)] if takes else []
+
     def reserve(self, limits):
         for lin in (self.proj, self.o, self.uq):
             if lin is not None:

@@ -126,10 +126,19 @@ class SinkAttention(Part):
         if self.v_mix == "blend":
             self.lam = float(tensors["v_mix"].float().item())
 
+    def native_builds(self):
+        """(library, defines) pairs compiled for this part's sizes, so that a model's first load builds them beside
+        its other libraries."""
+        takes = self.ctx.device.type == "cuda" and ops.sink_tc_takes(self.ctx.dtype, self.dim, self.vdim)
+        return [ops.sink_tc_library(self.dim, self.vdim)] if takes else []
+
     def reserve(self, limits):
         for lin in (self.qkv, self.o):
             if lin is not None:
                 lin.reserve(self.ctx.dtype, limits.max_tokens)
+        if self.ctx.device.type == "cuda" and ops.sink_tc_takes(self.ctx.dtype, self.dim, self.vdim):
+            from ..native.build import load_library
+            load_library(*ops.sink_tc_library(self.dim, self.vdim))        # built now, not inside the first step
 
     def forward(self, h, out, step, cache):
         n = h.shape[0]
@@ -145,7 +154,12 @@ class SinkAttention(Part):
                       self.vdim, {None: 0, "source": 1, "blend": 2}[self.v_mix], self.lam, v_first, cache.slots,
                       cache.tensor, cache.page_size)
         ctx = ws.rows("sink_ctx", n, self.heads * self.vdim, dt)
-        ops.sink_attention_simt(q, ctx, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
-                                self.kv_heads, self.dim, self.vdim, self.window, self.keep_first, self.scale,
-                                self.softcap, self.bucket_of, self.rel, self.sink, cache.page_size)
+        if ops.sink_tc_takes(dt, self.dim, self.vdim):        # bfloat16 and sizes the tensor-core kernel is built for
+            ops.sink_attention_tc(q, ctx, cache.tensor, cache.block_table, step, self.heads, self.kv_heads, self.dim,
+                                  self.vdim, self.window, self.keep_first, self.scale, self.softcap, self.bucket_of,
+                                  self.rel, self.sink, cache.page_size)
+        else:
+            ops.sink_attention_simt(q, ctx, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
+                                    self.kv_heads, self.dim, self.vdim, self.window, self.keep_first, self.scale,
+                                    self.softcap, self.bucket_of, self.rel, self.sink, cache.page_size)
         return self.o.forward(ctx, out, defer=True)

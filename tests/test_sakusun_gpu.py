@@ -379,6 +379,47 @@ def test_attention_kernel_on_scattered_pages_with_loud_keys_at_the_edges(dtype):
             assert float((got - want).abs().max()) <= tol * max(1.0, float(want.abs().max())), (t, h)
 
 
+def test_tensor_core_attention_equals_the_cuda_core_kernel_on_scattered_pages():
+    """A prompt portion over cached rows and a single token in one launch, pages in shuffled order; the pages between
+    the kept first tokens and the earliest window hold 1e4, as pages that went back do."""
+    from types import SimpleNamespace
+    from fastllm_py_b200.native import ops
+    from fastllm_py_b200.parts.sink_attention import distance_buckets
+
+    gen = torch.Generator().manual_seed(9)
+    for heads, kv_heads, dim, vdim, window, keep, cap in ((4, 2, 32, 64, 70, 9, 3.0), (2, 1, 64, 48, 0, 0, 0.0),
+                                                          (3, 3, 16, 16, 5, 130, 1.0), (8, 2, 128, 128, 200, 64, 50.0)):
+        page, n = 16, 330
+        bf = torch.bfloat16
+        cache, table, rows = _scattered_cache(n, page, kv_heads, dim + vdim, bf, gen)
+        table = torch.cat([table, table]).contiguous()
+        if window:                                                    # pages wholly between the kept tokens and every window
+            first_lo = 100 - window + 1
+            for pg in range(-(-keep // page), max(0, first_lo) // page):
+                cache[table[0, pg].item()] = 1.0e4
+        ctx, qlen = [100, 329], [150, 1]
+        positions = torch.tensor(list(range(100, 250)) + [329], dtype=torch.int32)
+        tok_req = torch.tensor([0] * 150 + [1], dtype=torch.int32)
+        q = (torch.randn(151, heads * dim, generator=gen) * 0.5).to(bf)
+        rel = torch.randn(12, heads, generator=gen)
+        sink = torch.randn(heads, generator=gen)
+        buckets = torch.tensor(distance_buckets(12, 300.0), dtype=torch.int32, device="cuda")
+        step = SimpleNamespace(req_start=torch.tensor([0, 150, 151], dtype=torch.int32, device="cuda"),
+                               req_ctx=torch.tensor(ctx, dtype=torch.int32, device="cuda"),
+                               req_qlen=torch.tensor(qlen, dtype=torch.int32, device="cuda"), n_requests=2)
+        got = torch.empty(151, heads * vdim, dtype=bf, device="cuda")
+        want = torch.empty_like(got)
+        table[1] = table[0]                                           # both requests read the same sequence's pages
+        ops.sink_attention_tc(q.cuda(), got, cache, table, step, heads, kv_heads, dim, vdim, window, keep, 0.2, cap,
+                              buckets, rel.cuda(), sink.cuda(), page)
+        ops.sink_attention_simt(q.cuda(), want, cache, table, tok_req.cuda(), positions.cuda(), heads, kv_heads, dim, vdim,
+                                window, keep, 0.2, cap, buckets, rel.cuda(), sink.cuda(), page)
+        torch.cuda.synchronize()
+        err = float((got.float() - want.float()).abs().max())
+        assert err <= 3e-2 * max(1.0, float(want.float().abs().max())), (heads, dim, vdim, err)
+        assert float(want.float().abs().max()) < 50.0                 # no poisoned row was read by either
+
+
 def test_distance_buckets_follow_the_oracle():
     from fastllm_py_b200.parts.sink_attention import distance_buckets
 

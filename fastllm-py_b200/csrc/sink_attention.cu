@@ -189,3 +189,216 @@ FL_API int fl_sink_attention_simt(const void* q, int q_dtype, long q_ld, void* o
                          kv_heads, dim, vdim, window, keep_first, scale, cap, bucket_of, n_dist, rel, sink)));
     return 0;
 }
+
+// ------------------------------------------------------------------ single tokens, keys split over blocks
+//   sink_decode         per (token, key/value head, split): the maxima, sums and weighted values of every query head
+//                       of the group over one split of 128 keys, so that a cache row is read once for the group.
+//                       The first `kept_splits` splits walk the kept first tokens (those the window has left behind),
+//                       the others the window from the multiple of 128 at or below its first key
+//   sink_decode_merge   per (token, query head): the splits and the sink added up
+#define SINK_SPLIT 128           // keys of a split: one per thread
+
+__device__ __forceinline__ void sink_load8(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void sink_load8(const bf16* p, float* v) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
+// GROUP: query heads per key/value head, rounded up to a power of two (at most 8).
+// partial: [n_decode][heads][n_splits][vdim + 2] floats: maximum, sum, weighted values.
+template <typename T, int GROUP>
+__global__ void __launch_bounds__(SINK_SPLIT) sink_decode_kernel(
+    const T* __restrict__ q, long q_ld, const T* __restrict__ cache, long page_stride, int page_size,
+    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req, const int* __restrict__ positions,
+    const int* __restrict__ decode_tokens, float* __restrict__ partial, int n_splits, int kept_splits, int heads,
+    int kv_heads, int dim, int vdim, int window, int keep_first, float scale, float cap, const int* __restrict__ bucket_of,
+    int n_dist, const float* __restrict__ rel, int vec8) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ __align__(16) unsigned char dec_smem[];
+    long* off_s = reinterpret_cast<long*>(dec_smem);                  // [SPLIT] element offset of each row's value part
+    float* p_s = reinterpret_cast<float*>(off_s + SINK_SPLIT);        // [SPLIT][GROUP] numerators
+    float* red_s = p_s + SINK_SPLIT * GROUP;                          // [4 warps][GROUP]
+    float* q_s = red_s + 4 * GROUP;                                   // [GROUP][dim]
+    const int t = decode_tokens[blockIdx.x], g = blockIdx.y, split = blockIdx.z, tid = threadIdx.x;
+    const int group = heads / kv_heads;
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int kept = window > 0 ? min(keep_first, lo) : 0;
+    // the split's keys: [first, first + 128) cut to [from, to)
+    int first, from, to;
+    if (split < kept_splits) {
+        first = split * SINK_SPLIT;
+        from = first;
+        to = min(first + SINK_SPLIT, kept);
+    } else {
+        first = (lo / SINK_SPLIT + (split - kept_splits)) * SINK_SPLIT;
+        from = max(first, lo);
+        to = min(first + SINK_SPLIT, pos + 1);
+    }
+    const int row_w = dim + vdim;
+    float* out = partial + (((long)blockIdx.x * heads + (long)g * group) * n_splits + split) * (vdim + 2);
+    const long h_stride = (long)n_splits * (vdim + 2);                // from one head to the next
+    if (from >= to) {                                                 // nothing of this token in the split
+        for (int hh = tid; hh < group; hh += SINK_SPLIT) {
+            out[hh * h_stride] = -CUDART_INF_F;
+            out[hh * h_stride + 1] = 0.0f;
+        }
+        return;
+    }
+    for (int i = tid; i < group * dim; i += SINK_SPLIT) q_s[i] = to_f32<T>(q[(long)t * q_ld + (long)g * group * dim + i]);
+    __syncthreads();
+    const int* bt = block_table + (long)tok_req[t] * bt_stride;
+    const int j = first + tid;
+    const bool valid = j >= from && j < to;
+    float s[GROUP];
+#pragma unroll
+    for (int hh = 0; hh < GROUP; ++hh) s[hh] = 0.0f;
+    if (valid) {
+        const long off = (long)bt[j / page_size] * page_stride + ((long)g * page_size + j % page_size) * row_w;
+        off_s[tid] = off + dim;
+        const T* kp = cache + off;
+        if (vec8) {
+            for (int d = 0; d < dim; d += 8) {
+                float k[8];
+                sink_load8(kp + d, k);
+#pragma unroll
+                for (int e = 0; e < 8; ++e)
+#pragma unroll
+                    for (int hh = 0; hh < GROUP; ++hh)
+                        if (hh < group) s[hh] += q_s[hh * dim + d + e] * k[e];
+            }
+        } else {
+            for (int d = 0; d < dim; ++d) {
+                const float k = to_f32<T>(kp[d]);
+#pragma unroll
+                for (int hh = 0; hh < GROUP; ++hh)
+                    if (hh < group) s[hh] += q_s[hh * dim + d] * k;
+            }
+        }
+    }
+    const int warp = tid >> 5, lane = tid & 31;
+    float m[GROUP];
+#pragma unroll
+    for (int hh = 0; hh < GROUP; ++hh) {
+        s[hh] = (valid && hh < group) ? sink_score(s[hh], scale, cap, bucket_of, n_dist, rel, heads, g * group + hh, pos - j)
+                                      : -CUDART_INF_F;
+        const float w = warp_max(s[hh]);
+        if (lane == 0) red_s[warp * GROUP + hh] = w;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int hh = 0; hh < GROUP; ++hh) {
+        m[hh] = fmaxf(fmaxf(red_s[hh], red_s[GROUP + hh]), fmaxf(red_s[2 * GROUP + hh], red_s[3 * GROUP + hh]));
+        const float p = (valid && hh < group) ? expf(s[hh] - m[hh]) : 0.0f;      // (some key of the split is valid: m is finite)
+        p_s[tid * GROUP + hh] = p;
+        s[hh] = warp_sum(p);
+    }
+    __syncthreads();                                                  // red_s was read; p_s and off_s are written
+#pragma unroll
+    for (int hh = 0; hh < GROUP; ++hh)
+        if (lane == 0) red_s[warp * GROUP + hh] = s[hh];
+    __syncthreads();
+#pragma unroll
+    for (int hh = 0; hh < GROUP; ++hh)
+        if (tid == hh && hh < group) {                                // (m is the same in every thread)
+            out[hh * h_stride] = m[hh];
+            out[hh * h_stride + 1] = red_s[hh] + red_s[GROUP + hh] + red_s[2 * GROUP + hh] + red_s[3 * GROUP + hh];
+        }
+    const int j_begin = from - first, j_end = to - first;
+    for (int d = tid; d < vdim; d += SINK_SPLIT) {
+        float acc[GROUP];
+#pragma unroll
+        for (int hh = 0; hh < GROUP; ++hh) acc[hh] = 0.0f;
+#pragma unroll 8
+        for (int jj = j_begin; jj < j_end; ++jj) {
+            const float v = to_f32<T>(cache[off_s[jj] + d]);
+#pragma unroll
+            for (int hh = 0; hh < GROUP; ++hh) acc[hh] += p_s[jj * GROUP + hh] * v;
+        }
+#pragma unroll
+        for (int hh = 0; hh < GROUP; ++hh)
+            if (hh < group) out[hh * h_stride + 2 + d] = acc[hh];
+    }
+}
+
+// One block per (token, query head): the splits and the sink added up.
+template <typename T>
+__global__ void __launch_bounds__(128) sink_decode_merge_kernel(const float* __restrict__ partial, int n_splits,
+                                                                const int* __restrict__ decode_tokens, T* __restrict__ out,
+                                                                long out_ld, int heads, int vdim,
+                                                                const float* __restrict__ sink) {
+    pdl_wait();
+    pdl_trigger();
+    const int h = blockIdx.y, tid = threadIdx.x;
+    const float* base = partial + ((long)blockIdx.x * heads + h) * n_splits * (vdim + 2);
+    float top = sink != nullptr ? sink[h] : -CUDART_INF_F;
+    for (int s = 0; s < n_splits; ++s) top = fmaxf(top, base[(long)s * (vdim + 2)]);
+    float sum = sink != nullptr ? expf(sink[h] - top) : 0.0f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float ms = base[(long)s * (vdim + 2)];
+        if (ms != -CUDART_INF_F) sum += base[(long)s * (vdim + 2) + 1] * expf(ms - top);
+    }
+    T* dst = out + (long)decode_tokens[blockIdx.x] * out_ld + (long)h * vdim;
+    for (int d = tid; d < vdim; d += 128) {
+        float a = 0.0f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = base[(long)s * (vdim + 2)];
+            if (ms != -CUDART_INF_F) a += base[(long)s * (vdim + 2) + 2 + d] * expf(ms - top);
+        }
+        dst[d] = from_f32<T>(a / sum);
+    }
+}
+
+// Whether the split-key kernels take a layer of these sizes.
+FL_API int fl_sink_decode_takes(int heads, int kv_heads, int dim, int vdim) {
+    const int group = kv_heads > 0 && heads % kv_heads == 0 ? heads / kv_heads : 0;
+    return group >= 1 && group <= 8 && vdim >= 1 && vdim <= 4096 && dim >= 1 &&
+           (size_t)SINK_SPLIT * (sizeof(long) + 8 * sizeof(float)) + (size_t)(32 + 8 * dim) * sizeof(float) <= 48 * 1024;
+}
+
+// The rows `decode_tokens` (n_decode of them, each the single token of its request) of q get attention over their
+// requests' cache rows.  kept_splits = ceil(keep_first / 128) (0 without a window); n_splits = kept_splits + enough
+// window splits to reach every token's last key: (longest visible span - 1) / 128 + 2 does.
+// partial: n_decode * heads * n_splits * (vdim + 2) floats.
+FL_API int fl_sink_decode(const void* q, int dtype, long q_ld, void* out, long out_ld, const void* cache, long page_stride,
+                          int page_size, const int* block_table, int bt_stride, const int* tok_req, const int* positions,
+                          const int* decode_tokens, int n_decode, float* partial, int n_splits, int kept_splits, int heads,
+                          int kv_heads, int dim, int vdim, int window, int keep_first, float scale, float cap,
+                          const int* bucket_of, int n_dist, const float* rel, const float* sink, cudaStream_t stream) {
+    if (n_decode <= 0) return 0;
+    if (!fl_sink_decode_takes(heads, kv_heads, dim, vdim) || n_splits < 1 || n_splits > 65535 || kv_heads > 65535 ||
+        kept_splits < 0 || kept_splits >= n_splits || (rel != nullptr && (bucket_of == nullptr || n_dist < 1)))
+        return (int)cudaErrorInvalidValue;
+    const int group = heads / kv_heads;
+    const int gp = group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8;
+    const size_t smem = (size_t)SINK_SPLIT * (sizeof(long) + gp * sizeof(float)) + (size_t)(4 * gp + gp * dim) * sizeof(float);
+    dim3 grid(n_decode, kv_heads, n_splits);
+    // (rows start 16 bytes aligned when the row and page sizes are multiples of 8 elements and the pool is aligned)
+    const int vec8 = dim % 8 == 0 && vdim % 8 == 0 && page_stride % 8 == 0 && ((uintptr_t)cache % 32) == 0;
+    int rc = 0;
+#define FL_SINK_DECODE(G)                                                                                            \
+    FL_DISPATCH(dtype, T, rc = fl_launch(sink_decode_kernel<T, G>, grid, dim3(SINK_SPLIT), smem, stream, (const T*)q, \
+                                         q_ld, (const T*)cache, page_stride, page_size, block_table, bt_stride,      \
+                                         tok_req, positions, decode_tokens, partial, n_splits, kept_splits, heads,   \
+                                         kv_heads, dim, vdim, window, keep_first, scale, cap, bucket_of, n_dist, rel, vec8))
+    if (gp == 1) { FL_SINK_DECODE(1); }
+    else if (gp == 2) { FL_SINK_DECODE(2); }
+    else if (gp == 4) { FL_SINK_DECODE(4); }
+    else { FL_SINK_DECODE(8); }
+#undef FL_SINK_DECODE
+    if (rc) return rc;
+    FL_DISPATCH(dtype, T, return fl_launch(sink_decode_merge_kernel<T>, dim3(n_decode, heads), dim3(128), 0, stream,
+                                           (const float*)partial, n_splits, decode_tokens, (T*)out, out_ld, heads, vdim,
+                                           sink));
+    return 0;
+}

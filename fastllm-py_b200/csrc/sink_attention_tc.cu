@@ -11,7 +11,8 @@
 // first key any of its rows' windows may see to the last; blocks in between are never touched (their pages may have
 // gone back).  Rows cached by earlier steps and the rows this step wrote are read alike, so a portion of a prompt
 // is the same as a whole prompt, and a single decoded token is a tile of one row (warps without rows only help to
-// load).  Key blocks start at multiples of 64 of the absolute position, so the partial maxima and sums a row goes
+// load; steps of single tokens have a kernel of their own that splits the keys, sink_attention.cu, and the launcher
+// can leave such requests out).  Key blocks start at multiples of 64 of the absolute position, so the partial maxima and sums a row goes
 // through depend on the row's position only.  A block's rows (key and value: one piece of memory per token) come by
 // cp.async into a two-stage ring while the block before is multiplied.  The bias of this head by distance is staged
 // in shared memory for the first SINK_NEAR distances; farther ones (kept tokens far behind) are looked up in global
@@ -74,7 +75,7 @@ __global__ void __launch_bounds__(STC_THREADS, 3) sink_attention_tc_kernel(
     const bf16* __restrict__ q, long q_ld, bf16* __restrict__ out, long out_ld, const bf16* __restrict__ cache,
     long page_stride, int page_size, int page_shift, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ req_start, const int* __restrict__ req_ctx, const int* __restrict__ req_qlen,
-    int n_requests, int heads, int kv_heads, int window, int keep_first, float scale, float cap,
+    int n_requests, int include_single, int heads, int kv_heads, int window, int keep_first, float scale, float cap,
     const int* __restrict__ row_of, int n_dist, const float* __restrict__ rel, const float* __restrict__ sink) {
     pdl_wait();
     pdl_trigger();
@@ -88,7 +89,8 @@ __global__ void __launch_bounds__(STC_THREADS, 3) sink_attention_tc_kernel(
     {
         int acc = 0;
         for (int r = 0; r < n_requests; ++r) {
-            const int nt = (req_qlen[r] + STC_BM - 1) / STC_BM;
+            const int ql = req_qlen[r];
+            const int nt = (ql > 1 || include_single) ? (ql + STC_BM - 1) / STC_BM : 0;
             if ((int)blockIdx.x < acc + nt) { req = r; tile = nt - 1 - ((int)blockIdx.x - acc); break; }
             acc += nt;
         }
@@ -204,7 +206,8 @@ __global__ void __launch_bounds__(STC_THREADS, 3) sink_attention_tc_kernel(
                     float v = -CUDART_INF_F;
                     if (seen) {
                         v = s[nt][e] * scale;
-                        if (cap > 0.0f) v = cap * tanhf(v * inv_cap);
+                        // tanh(y) = 1 - 2 / (exp(2 y) + 1): absolute error about 1e-7, two fast instructions
+                        if (cap > 0.0f) v = cap * (1.0f - __fdividef(2.0f, __expf(2.0f * v * inv_cap) + 1.0f));
                         v *= STC_LOG2E;
                         if (rel != nullptr) {
                             const int d = pr - j;
@@ -280,12 +283,13 @@ __global__ void __launch_bounds__(STC_THREADS, 3) sink_attention_tc_kernel(
 FL_API int fl_sink_attention_tc_dim() { return SINK_DIM; }
 FL_API int fl_sink_attention_tc_vdim() { return SINK_VDIM; }
 
-// Every request r of the step gets attention for its rows req_start[r] .. req_start[r] + req_qlen[r] - 1 at positions
+// Every request r of the step with req_qlen[r] > 1 (or >= 1 with include_single) gets attention for its rows req_start[r] .. req_start[r] + req_qlen[r] - 1 at positions
 // req_ctx[r] + i over its cached rows.  n_tokens bounds the number of 64-row tiles.  cap <= 0: no cap; rel null: no
 // bias; sink null: no sink; window <= 0: every earlier key.
 FL_API int fl_sink_attention_tc(const void* q, long q_ld, void* out, long out_ld, const void* cache, long page_stride,
                                 int page_size, const int* block_table, int bt_stride, const int* req_start,
-                                const int* req_ctx, const int* req_qlen, int n_requests, int n_tokens, int heads,
+                                const int* req_ctx, const int* req_qlen, int n_requests, int n_tokens,
+                                int include_single, int heads,
                                 int kv_heads, int window, int keep_first, float scale, float cap, const int* row_of,
                                 int n_dist, const float* rel, const float* sink, cudaStream_t stream) {
     if (n_requests <= 0 || n_tokens <= 0) return 0;
@@ -309,6 +313,6 @@ FL_API int fl_sink_attention_tc(const void* q, long q_ld, void* out, long out_ld
     dim3 grid(max_tiles, heads);
     return fl_launch(sink_attention_tc_kernel, grid, dim3(STC_THREADS), smem, stream, (const bf16*)q, q_ld, (bf16*)out,
                      out_ld, (const bf16*)cache, page_stride, page_size, page_shift, block_table, bt_stride, req_start,
-                     req_ctx, req_qlen, n_requests, heads, kv_heads, window, keep_first, scale, cap, row_of, n_dist, rel,
+                     req_ctx, req_qlen, n_requests, include_single, heads, kv_heads, window, keep_first, scale, cap, row_of, n_dist, rel,
                      sink);
 }

@@ -696,21 +696,59 @@ def sink_tc_library(dim: int, vdim: int):
 
 
 def sink_attention_tc(q, out, cache, block_table, step, heads, kv_heads, dim, vdim, window, keep_first, scale, cap,
-                      bucket_of, rel, sink, page_size):
+                      bucket_of, rel, sink, page_size, include_single=True):
     """`sink_attention_simt` on tensor cores: q, cache and out bfloat16; one build per (dim, vdim); 64 rows of a
-    request and one head per block, single tokens as tiles of one row."""
+    request and one head per block, single tokens as tiles of one row (left out with include_single=False)."""
     _require_cuda(q, out, cache, block_table, bucket_of, rel, sink)
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("sink_attention_tc: q, cache and out must be bfloat16")
     name, defines = sink_tc_library(dim, vdim)
     fn = _fn(name, "fl_sink_attention_tc", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_int,
-                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                             c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p], defines)
     _check(fn(_ptr(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), cache.stride(0), page_size, _ptr(block_table),
               block_table.stride(0), _ptr(step.req_start), _ptr(step.req_ctx), _ptr(step.req_qlen), step.n_requests,
-              q.shape[0], heads, kv_heads, int(window or 0), int(keep_first or 0), float(scale), float(cap or 0.0),
-              _ptr(bucket_of), 0 if bucket_of is None else bucket_of.numel(), _ptr(rel), _ptr(sink), _stream()),
-           "sink_attention_tc")
+              q.shape[0], int(include_single), heads, kv_heads, int(window or 0), int(keep_first or 0), float(scale),
+              float(cap or 0.0), _ptr(bucket_of), 0 if bucket_of is None else bucket_of.numel(), _ptr(rel), _ptr(sink),
+              _stream()), "sink_attention_tc")
+
+
+SINK_SPLIT = 128                 # keys of one split of the single-token kernel
+
+
+def sink_decode_takes(heads: int, kv_heads: int, dim: int, vdim: int) -> bool:
+    """Whether the split-key kernels for single tokens serve these sizes (up to eight query heads a key/value head)."""
+    fn = _fn("sink_attention", "fl_sink_decode_takes", [c_int, c_int, c_int, c_int])
+    return bool(fn(heads, kv_heads, dim, vdim))
+
+
+def sink_decode_splits(window, keep_first: int, longest: int):
+    """(splits in all, splits that walk the kept first tokens) for single tokens of sequences up to `longest`."""
+    kept = -(-int(keep_first or 0) // SINK_SPLIT) if window else 0
+    span = min(int(window), longest) if window else longest
+    return kept + (max(span, 1) - 1) // SINK_SPLIT + 2, kept
+
+
+def sink_decode(q, out, cache, block_table, tok_req, positions, decode_tokens, partial, n_splits, kept_splits, heads,
+                kv_heads, dim, vdim, window, keep_first, scale, cap, bucket_of, rel, sink, page_size):
+    """Sink attention for the rows `decode_tokens` of q (each the single token of its request): the keys split over
+    blocks of 128, every query head of a key/value head served by the block that reads its rows, then a merge with
+    the sink.  partial: float32, decode tokens * heads * n_splits * (vdim + 2)."""
+    _require_cuda(q, out, cache, block_table, tok_req, positions, decode_tokens, partial, bucket_of, rel, sink)
+    n = decode_tokens.numel()
+    if partial.dtype != torch.float32 or partial.numel() < n * heads * n_splits * (vdim + 2):
+        raise KernelError("sink_decode: the buffer for the splits' results is too small")
+    if q.dtype != cache.dtype or out.dtype != q.dtype:
+        raise KernelError("sink_decode: q, cache and out share a dtype")
+    fn = _fn("sink_attention", "fl_sink_decode",
+             [c_void_p, c_int, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_void_p,
+              c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p,
+              c_int, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(q), dtype_code(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), cache.stride(0), page_size,
+              _ptr(block_table), block_table.stride(0), _ptr(tok_req), _ptr(positions), _ptr(decode_tokens), n,
+              _ptr(partial), int(n_splits), int(kept_splits), heads, kv_heads, dim, vdim, int(window or 0),
+              int(keep_first or 0), float(scale), float(cap or 0.0), _ptr(bucket_of),
+              0 if bucket_of is None else bucket_of.numel(), _ptr(rel), _ptr(sink), _stream()), "sink_decode", 2)
 
 
 # ------------------------------------------------------------- routed experts

@@ -27,7 +27,7 @@ import math
 import torch
 
 from ..cache.needs import PagedKeysValues
-from ..native import ops
+from ..native import ops, scratch
 from .base import Part
 from .linear import Linear
 from .registry import register_part
@@ -59,6 +59,7 @@ class SinkAttention(Part):
     rel [B, heads]; with sink sink [heads]; for "blend" v_mix []."""
     category = "mixer"
     native_libraries = ("sink_attention",)
+    SCRATCH = "sink attention splits"
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
@@ -139,6 +140,35 @@ class SinkAttention(Part):
         if self.ctx.device.type == "cuda" and ops.sink_tc_takes(self.ctx.dtype, self.dim, self.vdim):
             from ..native.build import load_library
             load_library(*ops.sink_tc_library(self.dim, self.vdim))        # built now, not inside the first step
+        if self.ctx.device.type == "cuda" and self._splits_single_tokens():
+            longest = -(-limits.max_model_len // 1024) * 1024
+            self._partials(min(limits.max_tokens, limits.max_requests),
+                           ops.sink_decode_splits(self.window, self.keep_first, longest)[0])   # nothing grows under a graph
+
+    # ---- what the host decides per step: how many blocks share a single token's keys
+    @property
+    def plan_key(self):
+        return ("sink_attention", self.heads, self.kv_heads, self.dim, self.vdim, self.window, self.keep_first)
+
+    def _splits_single_tokens(self) -> bool:
+        """bfloat16 steps give their single tokens to the split-key kernels (the 32-bit path keeps one kernel for every
+        token, so that its sums do not depend on how a sequence was cut)."""
+        return self.ctx.dtype == torch.bfloat16 and ops.sink_decode_takes(self.heads, self.kv_heads, self.dim, self.vdim)
+
+    def plan_step(self, step):
+        if not self._splits_single_tokens() or step.n_decode_tokens == 0:
+            step.plans[self.plan_key] = (1, 0)
+            return
+        longest = step.max_seq_len
+        if step.for_graph:                                    # a captured step serves many: cover the length rounded up
+            longest = -(-longest // 1024) * 1024
+        step.plans[self.plan_key] = ops.sink_decode_splits(self.window, self.keep_first, longest)
+
+    def graph_key(self, step):
+        return step.plans.get(self.plan_key)
+
+    def _partials(self, n_tokens: int, n_splits: int):
+        return scratch.get(self.ctx.device, self.SCRATCH, n_tokens * self.heads * n_splits * (self.vdim + 2))
 
     def forward(self, h, out, step, cache):
         n = h.shape[0]
@@ -154,10 +184,23 @@ class SinkAttention(Part):
                       self.vdim, {None: 0, "source": 1, "blend": 2}[self.v_mix], self.lam, v_first, cache.slots,
                       cache.tensor, cache.page_size)
         ctx = ws.rows("sink_ctx", n, self.heads * self.vdim, dt)
-        if ops.sink_tc_takes(dt, self.dim, self.vdim):        # bfloat16 and sizes the tensor-core kernel is built for
+        tc = ops.sink_tc_takes(dt, self.dim, self.vdim)       # bfloat16 and sizes the tensor-core kernel is built for
+        # (where only the CUDA-core kernel serves prompt rows, a mixed step gives it every row)
+        single = step.n_decode_tokens if self._splits_single_tokens() and (tc or step.n_decode_tokens == n) else 0
+        if single:                                            # single tokens: their keys split over blocks
+            if self.plan_key not in step.plans:               # a step built by hand, not by the engine
+                self.plan_step(step)
+            n_splits, kept_splits = step.plans[self.plan_key]
+            ops.sink_decode(q, ctx, cache.tensor, cache.block_table, step.tok_req, step.positions, step.decode_tokens,
+                            self._partials(single, n_splits), n_splits, kept_splits, self.heads, self.kv_heads,
+                            self.dim, self.vdim, self.window, self.keep_first, self.scale, self.softcap, self.bucket_of,
+                            self.rel, self.sink, cache.page_size)
+        if single == n:
+            pass
+        elif tc:
             ops.sink_attention_tc(q, ctx, cache.tensor, cache.block_table, step, self.heads, self.kv_heads, self.dim,
                                   self.vdim, self.window, self.keep_first, self.scale, self.softcap, self.bucket_of,
-                                  self.rel, self.sink, cache.page_size)
+                                  self.rel, self.sink, cache.page_size, include_single=not single)
         else:
             ops.sink_attention_simt(q, ctx, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
                                     self.kv_heads, self.dim, self.vdim, self.window, self.keep_first, self.scale,

@@ -420,6 +420,41 @@ def test_tensor_core_attention_equals_the_cuda_core_kernel_on_scattered_pages():
         assert float(want.float().abs().max()) < 50.0                 # no poisoned row was read by either
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_split_key_kernel_for_single_tokens_equals_the_cuda_core_kernel(dtype):
+    """Single tokens at several depths of one sequence (before the window leaves the kept tokens behind, just after,
+    far after; at a split's first and last key), groups of one, three and eight query heads."""
+    from fastllm_py_b200.native import ops
+    from fastllm_py_b200.parts.sink_attention import distance_buckets
+
+    gen = torch.Generator().manual_seed(12)
+    for heads, kv_heads, dim, vdim, window, keep, cap in ((6, 2, 24, 40, 37, 6, 4.0), (8, 1, 64, 48, 150, 130, 50.0),
+                                                          (2, 2, 16, 200, 0, 0, 0.0), (4, 2, 8, 8, 300, 3, 1.0)):
+        page, n = 8, 700
+        cache, table, _ = _scattered_cache(n, page, kv_heads, dim + vdim, dtype, gen)
+        pos = [0, 1, 5, 36, 37, 43, 127, 128, 129, 255, 256, 300, 511, 640, 699]
+        positions = torch.tensor(pos, dtype=torch.int32).cuda()
+        tok_req = torch.zeros(len(pos), dtype=torch.int32).cuda()
+        rows = torch.arange(len(pos), dtype=torch.int32).cuda()
+        q = (torch.randn(len(pos), heads * dim, generator=gen) * 0.5).to(dtype).cuda()
+        rel = torch.randn(12, heads, generator=gen).cuda()
+        sink = torch.randn(heads, generator=gen).cuda()
+        buckets = torch.tensor(distance_buckets(12, 300.0), dtype=torch.int32, device="cuda")
+        n_splits, kept_splits = ops.sink_decode_splits(window, keep, 700)
+        partial = torch.empty(len(pos) * heads * n_splits * (vdim + 2), device="cuda")
+        got = torch.empty(len(pos), heads * vdim, dtype=dtype, device="cuda")
+        want = torch.empty_like(got)
+        assert ops.sink_decode_takes(heads, kv_heads, dim, vdim)
+        ops.sink_decode(q, got, cache, table, tok_req, positions, rows, partial, n_splits, kept_splits, heads, kv_heads,
+                        dim, vdim, window, keep, 0.2, cap, buckets, rel, sink, page)
+        ops.sink_attention_simt(q, want, cache, table, tok_req, positions, heads, kv_heads, dim, vdim, window, keep, 0.2,
+                                cap, buckets, rel, sink, page)
+        torch.cuda.synchronize()
+        err = float((got.float() - want.float()).abs().max())
+        tol = 2e-5 if dtype == torch.float32 else 2e-2
+        assert err <= tol * max(1.0, float(want.float().abs().max())), (heads, dim, vdim, err)
+
+
 def test_distance_buckets_follow_the_oracle():
     from fastllm_py_b200.parts.sink_attention import distance_buckets
 

@@ -21,7 +21,37 @@
 // All arithmetic is float; the residual stream is float in both precisions.
 #include "common.cuh"
 
-template <typename TO>
+// V consecutive channels a thread (4 where width, the row pitches and the bases allow 16-byte accesses, else 1): a row
+// is spread over gridDim.y blocks, so a step of a few rows still has its loads in flight side by side.  Every element
+// is the same chain of fused multiply-adds whichever form runs.
+template <int V> struct ConvRow { float v[V]; };
+
+template <int V> __device__ __forceinline__ ConvRow<V> conv_load(const float* p) {
+    ConvRow<V> r;
+    if constexpr (V == 4) {
+        const float4 q = *reinterpret_cast<const float4*>(p);
+        r.v[0] = q.x; r.v[1] = q.y; r.v[2] = q.z; r.v[3] = q.w;
+    } else {
+        r.v[0] = *p;
+    }
+    return r;
+}
+
+template <typename TO, int V> __device__ __forceinline__ void conv_store(TO* p, const ConvRow<V>& r) {
+    if constexpr (V == 4 && sizeof(TO) == 2) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(r.v[0], r.v[1]), hi = __floats2bfloat162_rn(r.v[2], r.v[3]);
+        uint2 q;
+        q.x = *reinterpret_cast<unsigned*>(&lo);
+        q.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(p) = q;
+    } else if constexpr (V == 4) {
+        *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+    } else {
+        p[0] = from_f32<TO>(r.v[0]);
+    }
+}
+
+template <typename TO, int V>
 __global__ void __launch_bounds__(256) input_conv_kernel(
     const float* __restrict__ x, long x_ld, const float* __restrict__ w, int taps, const float* __restrict__ ring,
     long ring_slot_stride, const int* __restrict__ positions, const int* __restrict__ tok_req,
@@ -30,26 +60,34 @@ __global__ void __launch_bounds__(256) input_conv_kernel(
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
+    const int i = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    if (i >= width) return;
     const int r = tok_req[t];
     const int pos = positions[t], start = req_start[r];
     const int back = taps - 1;
     const float* ring_r = ring != nullptr ? ring + (long)req_slot[r] * ring_slot_stride : nullptr;
-    const float* xr = x + (long)t * x_ld;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float xi = xr[i];
-        float acc = 0.0f;
-        for (int j = 0; j < taps; ++j) {
-            const int k = back - j;                        // rows back in time
-            float v;
-            if (k == 0) v = xi;
-            else if (pos - k < 0) v = 0.0f;
-            else if (t - k >= start) v = x[(long)(t - k) * x_ld + i];
-            else v = ring_r[(long)((pos - k) % back) * width + i];
-            acc = __fmaf_rn(w[(long)i * taps + j], v, acc);
-        }
-        if (h != nullptr) h[(long)t * h_ld + i] = from_f32<TO>(xi);
-        hc[(long)t * hc_ld + i] = from_f32<TO>(xi + acc);
+    const ConvRow<V> xi = conv_load<V>(x + (long)t * x_ld + i);
+    ConvRow<V> acc;
+#pragma unroll
+    for (int c = 0; c < V; ++c) acc.v[c] = 0.0f;
+    for (int j = 0; j < taps; ++j) {
+        const int k = back - j;                            // rows back in time
+        ConvRow<V> v;
+        if (k == 0) v = xi;
+        else if (pos - k < 0) continue;                    // zeros before the sequence's start (acc + w * 0 == acc)
+        else if (t - k >= start) v = conv_load<V>(x + (long)(t - k) * x_ld + i);
+        else v = conv_load<V>(ring_r + (long)((pos - k) % back) * width + i);
+#pragma unroll
+        for (int c = 0; c < V; ++c) acc.v[c] = __fmaf_rn(w[(long)(i + c) * taps + j], v.v[c], acc.v[c]);
     }
+    if (h != nullptr) conv_store<TO, V>(h + (long)t * h_ld + i, xi);
+#pragma unroll
+    for (int c = 0; c < V; ++c) acc.v[c] = xi.v[c] + acc.v[c];
+    conv_store<TO, V>(hc + (long)t * hc_ld + i, acc);
+}
+
+static inline bool fl_rows_take_vectors(const void* p, long ld, int elem_bytes) {
+    return p == nullptr || (((uintptr_t)p % (4 * elem_bytes)) == 0 && ld % 4 == 0);
 }
 
 // w: [width, taps] float; ring: [slots, >= (taps - 1) * width] float (may be null when taps == 1).
@@ -58,28 +96,49 @@ FL_API int fl_input_conv(const float* x, long x_ld, const float* w, int taps, co
                          long h_ld, void* hc, long hc_ld, int out_dtype, int n_tokens, int width, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (taps < 1 || (taps > 1 && ring == nullptr)) return (int)cudaErrorInvalidValue;
-    FL_DISPATCH(out_dtype, TO, return fl_launch(input_conv_kernel<TO>, dim3(n_tokens), dim3(256), 0, stream, x, x_ld, w, taps,
-                                                ring, ring_slot_stride, positions, tok_req, req_start, req_slot, (TO*)h,
-                                                h_ld, (TO*)hc, hc_ld, width));
+    FL_DISPATCH(out_dtype, TO, {
+        const bool vec = width % 4 == 0 && fl_rows_take_vectors(x, x_ld, 4) && fl_rows_take_vectors(ring, ring_slot_stride, 4) &&
+                         fl_rows_take_vectors(h, h_ld, sizeof(TO)) && fl_rows_take_vectors(hc, hc_ld, sizeof(TO));
+        if (vec)
+            return fl_launch(input_conv_kernel<TO, 4>, dim3(n_tokens, (width / 4 + 255) / 256), dim3(256), 0, stream, x, x_ld,
+                             w, taps, ring, ring_slot_stride, positions, tok_req, req_start, req_slot, (TO*)h, h_ld,
+                             (TO*)hc, hc_ld, width);
+        return fl_launch(input_conv_kernel<TO, 1>, dim3(n_tokens, (width + 255) / 256), dim3(256), 0, stream, x, x_ld, w,
+                         taps, ring, ring_slot_stride, positions, tok_req, req_start, req_slot, (TO*)h, h_ld, (TO*)hc,
+                         hc_ld, width);
+    });
     return 0;
 }
 
+// One block a row, blockDim a function of the width alone (so equal rows give equal sums wherever they sit).  y is
+// either a matrix of TD or, with y_splits > 0, the float partial sums of a product whose K was split: y_splits slabs
+// of [rows, y_ld] floats y_split_stride apart, added here in slab order and rounded to TD first (what the reduce
+// kernel would have written).
 template <typename TD>
-__global__ void __launch_bounds__(256) gated_norm_add_kernel(
-    float* __restrict__ x, long x_ld, const TD* __restrict__ y, long y_ld, const TD* __restrict__ gate, long gate_ld,
-    const float* __restrict__ gate_bias, const float* __restrict__ w, float eps, int width, float* __restrict__ ring,
-    long ring_slot_stride, int taps, const int* __restrict__ positions, const int* __restrict__ tok_req,
-    const int* __restrict__ req_start, const int* __restrict__ req_qlen, const int* __restrict__ req_slot) {
+__global__ void __launch_bounds__(1024) gated_norm_add_kernel(
+    float* __restrict__ x, long x_ld, const void* __restrict__ y, long y_ld, int y_splits, long y_split_stride,
+    const TD* __restrict__ gate, long gate_ld, const float* __restrict__ gate_bias, const float* __restrict__ w, float eps,
+    int width, float* __restrict__ ring, long ring_slot_stride, int taps, const int* __restrict__ positions,
+    const int* __restrict__ tok_req, const int* __restrict__ req_start, const int* __restrict__ req_qlen,
+    const int* __restrict__ req_slot) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float gated_row[];                   // [width]
     __shared__ float scratch[32];
     const int t = blockIdx.x;
-    const TD* yr = y + (long)t * y_ld;
+    const TD* yr = y_splits > 0 ? nullptr : (const TD*)y + (long)t * y_ld;
+    const float* yp = y_splits > 0 ? (const float*)y + (long)t * y_ld : nullptr;
     const TD* gr = gate != nullptr ? gate + (long)t * gate_ld : nullptr;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v = to_f32<TD>(yr[i]);
+        float v;
+        if (yp != nullptr) {
+            v = yp[i];
+            for (int s = 1; s < y_splits; ++s) v += yp[(long)s * y_split_stride + i];
+            v = to_f32<TD>(from_f32<TD>(v));
+        } else {
+            v = to_f32<TD>(yr[i]);
+        }
         if (gr != nullptr) {
             const float g = to_f32<TD>(gr[i]) + (gate_bias != nullptr ? gate_bias[i] : 0.0f);
             v = v / (1.0f + expf(-g));
@@ -103,22 +162,25 @@ __global__ void __launch_bounds__(256) gated_norm_add_kernel(
     }
 }
 
-// gate may be null (no gate); ring may be null (nothing to file).
-FL_API int fl_gated_norm_add(float* x, long x_ld, const void* y, long y_ld, const void* gate, long gate_ld, int dtype,
-                             const float* gate_bias, const float* w, float eps, int n_tokens, int width, float* ring,
-                             long ring_slot_stride, int taps, const int* positions, const int* tok_req,
-                             const int* req_start, const int* req_qlen, const int* req_slot, cudaStream_t stream) {
+// gate may be null (no gate); ring may be null (nothing to file).  y_splits 0: y is [n_tokens, width] of `dtype`.
+FL_API int fl_gated_norm_add(float* x, long x_ld, const void* y, long y_ld, int y_splits, long y_split_stride,
+                             const void* gate, long gate_ld, int dtype, const float* gate_bias, const float* w, float eps,
+                             int n_tokens, int width, float* ring, long ring_slot_stride, int taps, const int* positions,
+                             const int* tok_req, const int* req_start, const int* req_qlen, const int* req_slot,
+                             cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    int threads = 128;                                     // two elements a thread up to 2048 columns
+    while (threads < 1024 && threads * 2 < width) threads *= 2;
     FL_DISPATCH(dtype, TD, {
         if (smem > 48 * 1024) {
             cudaError_t e = cudaFuncSetAttribute(gated_norm_add_kernel<TD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        return fl_launch(gated_norm_add_kernel<TD>, dim3(n_tokens), dim3(256), smem, stream, x, x_ld, (const TD*)y, y_ld,
-                         (const TD*)gate, gate_ld, gate_bias, w, eps, width, ring, ring_slot_stride, taps, positions,
-                         tok_req, req_start, req_qlen, req_slot);
+        return fl_launch(gated_norm_add_kernel<TD>, dim3(n_tokens), dim3(threads), smem, stream, x, x_ld, y, y_ld, y_splits,
+                         y_split_stride, (const TD*)gate, gate_ld, gate_bias, w, eps, width, ring, ring_slot_stride, taps,
+                         positions, tok_req, req_start, req_qlen, req_slot);
     });
     return 0;
 }

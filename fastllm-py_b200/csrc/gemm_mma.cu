@@ -4,6 +4,8 @@
 // elements) and W is [batch][N][K].  This is the product per head that stands on either side of latent
 // attention (a head's query block through its own small matrix), for steps of any size: a block takes 64
 // rows x 128 columns of one batch entry, K in steps of 32 through a two-stage cp.async ring.
+// With `gate` (laid out like C: gate + b * g_batch, ldg between rows) the epilogue writes C * sigmoid(gate): the
+// product is rounded to C's type first, as a gate applied by a kernel of its own would have read it.
 // K must be a multiple of 32 and every A row 16-byte aligned; other shapes go to gemm_simt's batched form.
 #include "common.cuh"
 
@@ -20,7 +22,8 @@ __device__ __forceinline__ void gm_cp16(void* smem, const void* gmem) {
 template <typename TC>
 __global__ void __launch_bounds__(256) gemm_mma_batched_kernel(const bf16* __restrict__ A, long lda, long a_batch,
                                                                const bf16* __restrict__ W, TC* __restrict__ C, long ldc,
-                                                               long c_batch, int M, int N, int K) {
+                                                               long c_batch, int M, int N, int K,
+                                                               const TC* __restrict__ gate, long ldg, long g_batch) {
     pdl_wait();
     pdl_trigger();
     __shared__ __align__(16) bf16 a_s[2][GM_BM][GM_PITCH];
@@ -83,6 +86,7 @@ __global__ void __launch_bounds__(256) gemm_mma_batched_kernel(const bf16* __res
         __syncthreads();
     }
     TC* c_base = C + b * c_batch;
+    const TC* g_base = gate != nullptr ? gate + b * g_batch : nullptr;
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -94,7 +98,10 @@ __global__ void __launch_bounds__(256) gemm_mma_batched_kernel(const bf16* __res
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     const int n = n0 + wn * 32 + j * 8 + (lane & 3) * 2 + c;
-                    if (n < N) c_base[(long)m * ldc + n] = from_f32<TC>(acc[i][j][half * 2 + c]);
+                    if (n >= N) continue;
+                    TC v = from_f32<TC>(acc[i][j][half * 2 + c]);
+                    if (g_base != nullptr) v = from_f32<TC>(to_f32<TC>(v) / (1.0f + expf(-to_f32<TC>(g_base[(long)m * ldg + n]))));
+                    c_base[(long)m * ldc + n] = v;
                 }
         }
 }
@@ -104,13 +111,14 @@ FL_API int fl_gemm_mma_batched_takes(long lda, long a_batch, int K, const void* 
 }
 
 FL_API int fl_gemm_mma_batched(const void* A, long lda, long a_batch, const void* W, void* C, int c_dtype, long ldc,
-                               long c_batch, int M, int N, int K, int batch, cudaStream_t stream) {
+                               long c_batch, int M, int N, int K, int batch, const void* gate, long ldg, long g_batch,
+                               cudaStream_t stream) {
     if (M <= 0 || N <= 0 || batch <= 0) return 0;
     if (!fl_gemm_mma_batched_takes(lda, a_batch, K, A) || ((uintptr_t)W % 16) || batch > 65535 || (N + GM_BN - 1) / GM_BN > 65535)
         return (int)cudaErrorInvalidValue;
     dim3 grid((M + GM_BM - 1) / GM_BM, (N + GM_BN - 1) / GM_BN, batch);
     FL_DISPATCH(c_dtype, TC,
         return fl_launch(gemm_mma_batched_kernel<TC>, grid, dim3(256), 0, stream, (const bf16*)A, lda, a_batch,
-                         (const bf16*)W, (TC*)C, ldc, c_batch, M, N, K));
+                         (const bf16*)W, (TC*)C, ldc, c_batch, M, N, K, (const TC*)gate, ldg, g_batch));
     return 0;
 }

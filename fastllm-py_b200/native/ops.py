@@ -571,19 +571,24 @@ def gemm_simt_batched(a, a_batch, w, out, out_batch):
               _ld(out), out_batch, a.shape[0], n, k, batch, _stream()), "gemm_simt_batched")
 
 
-def gemm_batched(a, a_batch, w, out, out_batch):
+def gemm_batched(a, a_batch, w, out, out_batch, gate=None):
     """`gemm_simt_batched` with the kernel chosen by the operands: bfloat16 a and w with K a multiple of 32
-    and 16-byte aligned column blocks go to the tensor cores, everything else to the CUDA cores."""
+    and 16-byte aligned column blocks go to the tensor cores, everything else to the CUDA cores.  `gate` (shaped and
+    typed like `out`): out *= sigmoid(gate), in the tensor-core kernel's epilogue or by a kernel of its own."""
     batch, n, k = w.shape
     if a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 32 == 0 and a_batch % 8 == 0 \
             and _ld(a) % 8 == 0 and a.data_ptr() % 16 == 0 and w.is_contiguous():
-        _require_cuda(a, w, out)
+        _require_cuda(a, w, out, gate)
+        if gate is not None and (gate.dtype != out.dtype or gate.shape != out.shape):
+            raise KernelError("gemm_batched: the gate shares the output's shape and dtype")
         fn = _fn("gemm_mma", "fl_gemm_mma_batched", [c_void_p, c_long, c_long, c_void_p, c_void_p, c_int, c_long, c_long,
-                                                     c_int, c_int, c_int, c_int, c_void_p])
+                                                     c_int, c_int, c_int, c_int, c_void_p, c_long, c_long, c_void_p])
         _check(fn(_ptr(a), _ld(a), a_batch, _ptr(w), _ptr(out), dtype_code(out), _ld(out), out_batch, a.shape[0], n, k,
-                  batch, _stream()), "gemm_mma_batched")
+                  batch, _ptr(gate), 0 if gate is None else _ld(gate), out_batch, _stream()), "gemm_mma_batched")
         return
     gemm_simt_batched(a, a_batch, w, out, out_batch)
+    if gate is not None:
+        sigmoid_gate(out, gate)
 
 
 # ------------------------------------------ post-norm block with input convolution; paired-token embedding
@@ -606,16 +611,26 @@ def input_conv(x, w, taps, ring, step, h, hc):
 
 
 def gated_norm_add(x, y, gate, gate_bias, w, eps, step, ring=None, taps=1):
-    """x += rmsnorm(y * sigmoid(gate + gate_bias)) * w (no gate: rmsnorm(y) * w).  With `ring`, the rows of x as they
-    were before the add are filed for the request's last taps - 1 rows of the step (see `input_conv`)."""
-    _require_cuda(x, y, gate, gate_bias, w, ring)
-    if x.dtype != torch.float32 or w.dtype != torch.float32 or (gate is not None and gate.dtype != y.dtype) or \
-            (gate_bias is not None and gate_bias.dtype != torch.float32):
+    """x += rmsnorm(y * sigmoid(gate + gate_bias)) * w (no gate: rmsnorm(y) * w).  y is a matrix, or a product left as
+    split-K partial sums (`gemm_tc.Partial`), which the kernel adds up as it reads them and rounds to `gate`'s dtype.
+    With `ring`, the rows of x as they were before the add are filed for the request's last taps - 1 rows of the step
+    (see `input_conv`)."""
+    partial = not isinstance(y, torch.Tensor)
+    if partial:
+        y.check()
+        if gate is None or (y.rows, y.cols) != tuple(x.shape):
+            raise KernelError("gated_norm_add: partial sums need a gate (it names the dtype) and the stream's shape")
+        y_data, y_ld, y_splits, y_stride, code = y.data, y.ld, y.splits, y.split_stride, dtype_code(gate)
+    else:
+        y_data, y_ld, y_splits, y_stride, code = y, _ld(y), 0, 0, dtype_code(y)
+    _require_cuda(x, y_data, gate, gate_bias, w, ring)
+    if x.dtype != torch.float32 or w.dtype != torch.float32 or (gate is not None and not partial and gate.dtype != y.dtype) \
+            or (gate_bias is not None and gate_bias.dtype != torch.float32):
         raise KernelError("gated_norm_add: float32 stream, weights and bias; gate of the sublayer output's dtype")
-    fn = _fn("gated_block", "fl_gated_norm_add", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p,
-                                                  c_void_p, c_float, c_int, c_int, c_void_p, c_long, c_int, c_void_p,
-                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
-    _check(fn(_ptr(x), _ld(x), _ptr(y), _ld(y), _ptr(gate), 0 if gate is None else _ld(gate), dtype_code(y),
+    fn = _fn("gated_block", "fl_gated_norm_add", [c_void_p, c_long, c_void_p, c_long, c_int, c_long, c_void_p, c_long, c_int,
+                                                  c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_long, c_int,
+                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(x), _ld(x), _ptr(y_data), y_ld, y_splits, y_stride, _ptr(gate), 0 if gate is None else _ld(gate), code,
               _ptr(gate_bias), _ptr(w), float(eps), x.shape[0], x.shape[1], _ptr(ring),
               0 if ring is None else ring.stride(0), int(taps), _ptr(step.positions), _ptr(step.tok_req),
               _ptr(step.req_start), _ptr(step.req_qlen), _ptr(step.req_slot), _stream()), "gated_norm_add")

@@ -225,16 +225,16 @@ class GatedPostNormBlock(Part):
         h = ws.rows("normed", n, self.hidden, dt) if self.gated else None
         hc = ws.rows("conv_in", n, self.hidden, dt)
         ops.input_conv(stream.x, self.conv[s], taps, ring, step, h, hc)
+        gate = None
+        if self.gated:                                        # before the sublayer: its last product may then stay
+            gate = ws.rows("branch_gate", n, self.hidden, dt)  # split-K partial sums until the kernel below adds them
+            self.gate[s].forward(h, gate)
         delta = ws.rows("delta", n, self.hidden, dt)
         left = run(hc, delta)
-        if left is not None:
-            left.reduce_into(delta)
-        gate = None
-        if self.gated:
-            gate = ws.rows("branch_gate", n, self.hidden, dt)
-            self.gate[s].forward(h, gate)
-        ops.gated_norm_add(stream.x, delta, gate, self.gate_bias.get(s), self._out_weight(s, norm), norm.eps, step,
-                           ring, taps)
+        if left is not None and not self.gated:
+            left = left.reduce_into(delta)
+        ops.gated_norm_add(stream.x, delta if left is None else left, gate, self.gate_bias.get(s),
+                           self._out_weight(s, norm), norm.eps, step, ring, taps)
 
     def forward(self, stream, step, cache, state=None):
         stream.settle()                                       # the sublayers read x itself

@@ -202,7 +202,6 @@ class LatentAttention(Part):
             ops.latent_attention(q, mix, cache.tensor, cache.block_table, step.tok_req, step.positions, self.heads,
                                  self.rank, self.rot, self.window, self.scale, cache.page_size)
         ctx = ws.rows("latent_ctx", n, self.heads * self.vdim, dt)
-        ops.gemm_batched(mix, self.rank, self.uv, ctx, self.vdim)
-        if self.out_gate:
-            ops.sigmoid_gate(ctx, ws.rows("latent_proj", n, cols, dt)[:, first + kv_cols:])
+        ops.gemm_batched(mix, self.rank, self.uv, ctx, self.vdim,
+                         gate=ws.rows("latent_proj", n, cols, dt)[:, first + kv_cols:] if self.out_gate else None)
         return self.o.forward(ctx, out, defer=True)

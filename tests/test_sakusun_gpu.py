@@ -465,14 +465,15 @@ def test_distance_buckets_follow_the_oracle():
         assert table[-1] == rows - 1 and table[0] == 0
 
 
-def test_block_kernels_carry_rows_from_step_to_step():
+@pytest.mark.parametrize("width, taps", [(20, 4), (18, 3), (1300, 2), (4100, 5)])
+def test_block_kernels_carry_rows_from_step_to_step(width, taps):
     """input_conv + gated_norm_add over three steps of two requests with unequal portions (one of them a single
-    token at a time) against a whole-sequence computation in float64; the ring is filed by position."""
+    token at a time) against a whole-sequence computation in float64; the ring is filed by position.  Widths that
+    take four channels a thread and one, and rows wider than a block."""
     from types import SimpleNamespace
     from fastllm_py_b200.native import ops
 
     gen = torch.Generator().manual_seed(4)
-    width, taps = 20, 4
     w = torch.randn(width, taps, generator=gen)
     gate_w = torch.randn(width, generator=gen)
     bias = torch.randn(width, generator=gen)
@@ -510,7 +511,7 @@ def test_block_kernels_carry_rows_from_step_to_step():
         for k, (r, i) in enumerate(rows):
             z = ys[r][i].double() * torch.sigmoid(gs[r][i].double() + bias.double())
             want = xs[r][i].double() + z / torch.sqrt((z * z).mean() + 1e-5) * gate_w.double()
-            assert torch.allclose(x[k].double().cpu(), want, atol=1e-5), (r, i)
+            assert torch.allclose(x[k].double().cpu(), want, atol=2e-5), (r, i)
         for r, n in portions.items():
             done[r] += n
 
@@ -545,3 +546,49 @@ def test_pair_embedding_keeps_the_last_token_of_a_request():
                 k += 1
             done[r] += n
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gated_norm_add_adds_up_partial_sums_like_the_reduce_kernel(dtype):
+    """A product left as split-K slabs gives, bit for bit, what the reduce kernel followed by the plain form gives."""
+    from types import SimpleNamespace
+    from fastllm_py_b200.native import ops
+    from fastllm_py_b200.native.gemm_tc import Partial
+
+    gen = torch.Generator().manual_seed(9)
+    n, width, splits, ld = 5, 70, 3, 72
+    slabs = torch.randn(splits, n, ld, generator=gen).cuda()
+    gate = torch.randn(n, width, generator=gen).cuda().to(dtype)
+    bias, w = torch.randn(width, generator=gen).cuda(), torch.randn(width, generator=gen).cuda()
+    dev = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    step = SimpleNamespace(positions=dev(list(range(n))), tok_req=dev([0] * n), req_start=dev([0, n]), req_qlen=dev([n]),
+                           req_slot=dev([0]))
+    x0 = torch.randn(n, width, generator=gen).cuda()
+    part = Partial(slabs, splits, n, width, ld, slabs.device)
+    y = torch.empty(n, width, device="cuda", dtype=dtype)
+    part.reduce_into(y)
+    a, b = x0.clone(), x0.clone()
+    ops.gated_norm_add(a, y, gate, bias, w, 1e-6, step)
+    ops.gated_norm_add(b, part, gate, bias, w, 1e-6, step)
+    assert torch.equal(a, b)
+    z = slabs.double().sum(0)[:, :width].to(dtype).double() * torch.sigmoid(gate.double() + bias.double())
+    want = x0.double() + z / torch.sqrt((z * z).mean(-1, keepdim=True) + 1e-6) * w.double()
+    assert torch.allclose(a.double(), want, atol=2e-5 if dtype == torch.float32 else 2e-2)
+
+
+def test_gate_in_the_per_head_product_equals_the_gate_kernel():
+    from fastllm_py_b200.native import ops
+
+    gen = torch.Generator().manual_seed(10)
+    n, heads, k, vd = 70, 3, 64, 40
+    a = torch.randn(n, heads * k, generator=gen).cuda().bfloat16()
+    w = (torch.randn(heads, vd, k, generator=gen) / 8).cuda().bfloat16()
+    wide = torch.randn(n, 16 + heads * vd, generator=gen).cuda().bfloat16()
+    gate = wide[:, 16:]                                       # a column block of a wider buffer, as in the mixer
+    plain_out, fused = torch.empty(n, heads * vd, device="cuda", dtype=torch.bfloat16), torch.empty(n, heads * vd, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_batched(a, k, w, plain_out, vd)
+    ops.sigmoid_gate(plain_out, gate)
+    ops.gemm_batched(a, k, w, fused, vd, gate=gate)
+    assert torch.equal(plain_out, fused)
+    want = torch.einsum("nhk,hvk->nhv", a.double().view(n, heads, k), w.double()).reshape(n, -1) * torch.sigmoid(gate.double())
+    assert torch.allclose(fused.double(), want, atol=3e-2, rtol=2e-2)

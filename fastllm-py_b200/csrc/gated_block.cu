@@ -114,7 +114,22 @@ FL_API int fl_input_conv(const float* x, long x_ld, const float* w, int taps, co
 // either a matrix of TD or, with y_splits > 0, the float partial sums of a product whose K was split: y_splits slabs
 // of [rows, y_ld] floats y_split_stride apart, added here in slab order and rounded to TD first (what the reduce
 // kernel would have written).
-template <typename TD>
+template <typename TD, int V> __device__ __forceinline__ ConvRow<V> td_load(const TD* p) {
+    ConvRow<V> r;
+    if constexpr (V == 4 && sizeof(TD) == 2) {
+        const uint2 q = *reinterpret_cast<const uint2*>(p);
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&q.y));
+        r.v[0] = lo.x; r.v[1] = lo.y; r.v[2] = hi.x; r.v[3] = hi.y;
+    } else if constexpr (V == 4) {
+        r = conv_load<4>(reinterpret_cast<const float*>(p));
+    } else {
+        r.v[0] = to_f32<TD>(p[0]);
+    }
+    return r;
+}
+
+template <typename TD, int V>
 __global__ void __launch_bounds__(1024) gated_norm_add_kernel(
     float* __restrict__ x, long x_ld, const void* __restrict__ y, long y_ld, int y_splits, long y_split_stride,
     const TD* __restrict__ gate, long gate_ld, const float* __restrict__ gate_bias, const float* __restrict__ w, float eps,
@@ -123,28 +138,40 @@ __global__ void __launch_bounds__(1024) gated_norm_add_kernel(
     const int* __restrict__ req_slot) {
     pdl_wait();
     pdl_trigger();
-    extern __shared__ float gated_row[];                   // [width]
+    extern __shared__ __align__(16) float gated_row[];     // [width]
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     const TD* yr = y_splits > 0 ? nullptr : (const TD*)y + (long)t * y_ld;
     const float* yp = y_splits > 0 ? (const float*)y + (long)t * y_ld : nullptr;
     const TD* gr = gate != nullptr ? gate + (long)t * gate_ld : nullptr;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float v;
+    for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) {
+        ConvRow<V> v;
         if (yp != nullptr) {
-            v = yp[i];
-            for (int s = 1; s < y_splits; ++s) v += yp[(long)s * y_split_stride + i];
-            v = to_f32<TD>(from_f32<TD>(v));
+            v = conv_load<V>(yp + i);
+            for (int s = 1; s < y_splits; ++s) {
+                const ConvRow<V> p = conv_load<V>(yp + (long)s * y_split_stride + i);
+#pragma unroll
+                for (int c = 0; c < V; ++c) v.v[c] += p.v[c];
+            }
+#pragma unroll
+            for (int c = 0; c < V; ++c) v.v[c] = to_f32<TD>(from_f32<TD>(v.v[c]));
         } else {
-            v = to_f32<TD>(yr[i]);
+            v = td_load<TD, V>(yr + i);
         }
         if (gr != nullptr) {
-            const float g = to_f32<TD>(gr[i]) + (gate_bias != nullptr ? gate_bias[i] : 0.0f);
-            v = v / (1.0f + expf(-g));
+            const ConvRow<V> g = td_load<TD, V>(gr + i);
+#pragma unroll
+            for (int c = 0; c < V; ++c) {
+                const float z = g.v[c] + (gate_bias != nullptr ? gate_bias[i + c] : 0.0f);
+                v.v[c] = v.v[c] / (1.0f + expf(-z));
+            }
         }
-        gated_row[i] = v;
-        ss += v * v;
+#pragma unroll
+        for (int c = 0; c < V; ++c) {
+            gated_row[i + c] = v.v[c];
+            ss += v.v[c] * v.v[c];
+        }
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
@@ -155,10 +182,13 @@ __global__ void __launch_bounds__(1024) gated_norm_add_kernel(
         if (t >= req_start[r] + req_qlen[r] - (taps - 1))
             file = ring + (long)req_slot[r] * ring_slot_stride + (long)(positions[t] % (taps - 1)) * width;
     }
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float xi = xr[i];
-        if (file != nullptr) file[i] = xi;
-        xr[i] = xi + gated_row[i] * inv * w[i];
+    for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) {
+        ConvRow<V> xi = conv_load<V>(xr + i);
+        const ConvRow<V> wi = conv_load<V>(w + i);
+        if (file != nullptr) conv_store<float, V>(file + i, xi);
+#pragma unroll
+        for (int c = 0; c < V; ++c) xi.v[c] = xi.v[c] + gated_row[i + c] * inv * wi.v[c];
+        conv_store<float, V>(xr + i, xi);
     }
 }
 
@@ -171,16 +201,25 @@ FL_API int fl_gated_norm_add(float* x, long x_ld, const void* y, long y_ld, int 
     if (n_tokens <= 0) return 0;
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
-    int threads = 128;                                     // two elements a thread up to 2048 columns
-    while (threads < 1024 && threads * 2 < width) threads *= 2;
     FL_DISPATCH(dtype, TD, {
+        // four channels a thread where every row takes 16-byte (8-byte for bfloat16) accesses; which form runs, and
+        // with how many threads, depends on the layer's width and buffers only, never on the step
+        const int y_bytes = y_splits > 0 ? 4 : (int)sizeof(TD);
+        const bool vec = width % 4 == 0 && fl_rows_take_vectors(x, x_ld, 4) && fl_rows_take_vectors(y, y_ld, y_bytes) &&
+                         y_split_stride % 4 == 0 && fl_rows_take_vectors(gate, gate_ld, sizeof(TD)) &&
+                         fl_rows_take_vectors(ring, ring_slot_stride, 4) && fl_rows_take_vectors(w, 4, 4) &&
+                         fl_rows_take_vectors(gate_bias, 4, 4);
+        const int per_thread = vec ? 4 : 2;
+        int threads = 64;
+        while (threads < 1024 && threads * per_thread < width) threads *= 2;
+        auto kernel = vec ? gated_norm_add_kernel<TD, 4> : gated_norm_add_kernel<TD, 1>;
         if (smem > 48 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(gated_norm_add_kernel<TD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        return fl_launch(gated_norm_add_kernel<TD>, dim3(n_tokens), dim3(threads), smem, stream, x, x_ld, y, y_ld, y_splits,
-                         y_split_stride, (const TD*)gate, gate_ld, gate_bias, w, eps, width, ring, ring_slot_stride, taps,
-                         positions, tok_req, req_start, req_qlen, req_slot);
+        return fl_launch(kernel, dim3(n_tokens), dim3(threads), smem, stream, x, x_ld, y, y_ld, y_splits, y_split_stride,
+                         (const TD*)gate, gate_ld, gate_bias, w, eps, width, ring, ring_slot_stride, taps, positions,
+                         tok_req, req_start, req_qlen, req_slot);
     });
     return 0;
 }

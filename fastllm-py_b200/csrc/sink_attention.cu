@@ -268,7 +268,20 @@ __global__ void __launch_bounds__(SINK_SPLIT) sink_decode_kernel(
         off_s[tid] = off + dim;
         const T* kp = cache + off;
         if (vec8) {
-            for (int d = 0; d < dim; d += 8) {
+            int d = 0;
+            for (; d + 32 <= dim; d += 32) {                          // four loads in flight before the first is used
+                float k[4][8];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) sink_load8(kp + d + u * 8, k[u]);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e)
+#pragma unroll
+                        for (int hh = 0; hh < GROUP; ++hh)
+                            if (hh < group) s[hh] += q_s[hh * dim + d + u * 8 + e] * k[u][e];
+            }
+            for (; d < dim; d += 8) {
                 float k[8];
                 sink_load8(kp + d, k);
 #pragma unroll
@@ -319,8 +332,19 @@ __global__ void __launch_bounds__(SINK_SPLIT) sink_decode_kernel(
         float acc[GROUP];
 #pragma unroll
         for (int hh = 0; hh < GROUP; ++hh) acc[hh] = 0.0f;
-#pragma unroll 8
-        for (int jj = j_begin; jj < j_end; ++jj) {
+        int jj = j_begin;
+        for (; jj + 16 <= j_end; jj += 16) {                          // sixteen rows' loads in flight together
+            T raw[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) raw[u] = cache[off_s[jj + u] + d];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+                const float v = to_f32<T>(raw[u]);
+#pragma unroll
+                for (int hh = 0; hh < GROUP; ++hh) acc[hh] += p_s[(jj + u) * GROUP + hh] * v;
+            }
+        }
+        for (; jj < j_end; ++jj) {
             const float v = to_f32<T>(cache[off_s[jj] + d]);
 #pragma unroll
             for (int hh = 0; hh < GROUP; ++hh) acc[hh] += p_s[jj * GROUP + hh] * v;

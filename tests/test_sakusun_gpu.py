@@ -548,15 +548,16 @@ def test_pair_embedding_keeps_the_last_token_of_a_request():
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("width", [70, 72, 2052])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_gated_norm_add_adds_up_partial_sums_like_the_reduce_kernel(dtype):
+def test_gated_norm_add_adds_up_partial_sums_like_the_reduce_kernel(dtype, width):
     """A product left as split-K slabs gives, bit for bit, what the reduce kernel followed by the plain form gives."""
     from types import SimpleNamespace
     from fastllm_py_b200.native import ops
     from fastllm_py_b200.native.gemm_tc import Partial
 
     gen = torch.Generator().manual_seed(9)
-    n, width, splits, ld = 5, 70, 3, 72
+    n, splits, ld = 5, 3, -(-width // 4) * 4
     slabs = torch.randn(splits, n, ld, generator=gen).cuda()
     gate = torch.randn(n, width, generator=gen).cuda().to(dtype)
     bias, w = torch.randn(width, generator=gen).cuda(), torch.randn(width, generator=gen).cuda()

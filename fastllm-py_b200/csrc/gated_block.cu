@@ -113,7 +113,7 @@ FL_API int fl_input_conv(const float* x, long x_ld, const float* w, int taps, co
 // One block a row, blockDim a function of the width alone (so equal rows give equal sums wherever they sit).  y is
 // either a matrix of TD or, with y_splits > 0, the float partial sums of a product whose K was split: y_splits slabs
 // of [rows, y_ld] floats y_split_stride apart, added here in slab order and rounded to TD first (what the reduce
-// kernel would have written).
+// kernel would have written).  The gate likewise, with g_splits.
 template <typename TD, int V> __device__ __forceinline__ ConvRow<V> td_load(const TD* p) {
     ConvRow<V> r;
     if constexpr (V == 4 && sizeof(TD) == 2) {
@@ -132,8 +132,8 @@ template <typename TD, int V> __device__ __forceinline__ ConvRow<V> td_load(cons
 template <typename TD, int V>
 __global__ void __launch_bounds__(1024) gated_norm_add_kernel(
     float* __restrict__ x, long x_ld, const void* __restrict__ y, long y_ld, int y_splits, long y_split_stride,
-    const TD* __restrict__ gate, long gate_ld, const float* __restrict__ gate_bias, const float* __restrict__ w, float eps,
-    int width, float* __restrict__ ring, long ring_slot_stride, int taps, const int* __restrict__ positions,
+    const void* __restrict__ gate, long gate_ld, int g_splits, long g_split_stride, const float* __restrict__ gate_bias,
+    const float* __restrict__ w, float eps, int width, float* __restrict__ ring, long ring_slot_stride, int taps, const int* __restrict__ positions,
     const int* __restrict__ tok_req, const int* __restrict__ req_start, const int* __restrict__ req_qlen,
     const int* __restrict__ req_slot) {
     pdl_wait();
@@ -143,7 +143,18 @@ __global__ void __launch_bounds__(1024) gated_norm_add_kernel(
     const int t = blockIdx.x;
     const TD* yr = y_splits > 0 ? nullptr : (const TD*)y + (long)t * y_ld;
     const float* yp = y_splits > 0 ? (const float*)y + (long)t * y_ld : nullptr;
-    const TD* gr = gate != nullptr ? gate + (long)t * gate_ld : nullptr;
+    const TD* gr = (gate != nullptr && g_splits == 0) ? (const TD*)gate + (long)t * gate_ld : nullptr;
+    const float* gp = (gate != nullptr && g_splits > 0) ? (const float*)gate + (long)t * gate_ld : nullptr;
+    float* xr = x + (long)t * x_ld;
+    // a row that one pass of the block covers (the usual case): x and the weight are asked for before the sum's
+    // barrier, so the row's loads are all in flight together; the arithmetic is the same either way
+    const bool one_pass = (int)blockDim.x * V >= width;
+    const int i0 = threadIdx.x * V;
+    ConvRow<V> x0, w0;
+    if (one_pass && i0 < width) {
+        x0 = conv_load<V>(xr + i0);
+        w0 = conv_load<V>(w + i0);
+    }
     float ss = 0.0f;
     for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) {
         ConvRow<V> v;
@@ -159,8 +170,20 @@ __global__ void __launch_bounds__(1024) gated_norm_add_kernel(
         } else {
             v = td_load<TD, V>(yr + i);
         }
-        if (gr != nullptr) {
-            const ConvRow<V> g = td_load<TD, V>(gr + i);
+        if (gr != nullptr || gp != nullptr) {
+            ConvRow<V> g;
+            if (gp != nullptr) {
+                g = conv_load<V>(gp + i);
+                for (int s = 1; s < g_splits; ++s) {
+                    const ConvRow<V> p = conv_load<V>(gp + (long)s * g_split_stride + i);
+#pragma unroll
+                    for (int c = 0; c < V; ++c) g.v[c] += p.v[c];
+                }
+#pragma unroll
+                for (int c = 0; c < V; ++c) g.v[c] = to_f32<TD>(from_f32<TD>(g.v[c]));
+            } else {
+                g = td_load<TD, V>(gr + i);
+            }
 #pragma unroll
             for (int c = 0; c < V; ++c) {
                 const float z = g.v[c] + (gate_bias != nullptr ? gate_bias[i + c] : 0.0f);
@@ -175,7 +198,6 @@ __global__ void __launch_bounds__(1024) gated_norm_add_kernel(
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)width + eps);
-    float* xr = x + (long)t * x_ld;
     float* file = nullptr;
     if (ring != nullptr && taps > 1) {
         const int r = tok_req[t];
@@ -183,8 +205,8 @@ __global__ void __launch_bounds__(1024) gated_norm_add_kernel(
             file = ring + (long)req_slot[r] * ring_slot_stride + (long)(positions[t] % (taps - 1)) * width;
     }
     for (int i = threadIdx.x * V; i < width; i += blockDim.x * V) {
-        ConvRow<V> xi = conv_load<V>(xr + i);
-        const ConvRow<V> wi = conv_load<V>(w + i);
+        ConvRow<V> xi = one_pass ? x0 : conv_load<V>(xr + i);
+        const ConvRow<V> wi = one_pass ? w0 : conv_load<V>(w + i);
         if (file != nullptr) conv_store<float, V>(file + i, xi);
 #pragma unroll
         for (int c = 0; c < V; ++c) xi.v[c] = xi.v[c] + gated_row[i + c] * inv * wi.v[c];
@@ -192,9 +214,11 @@ __global__ void __launch_bounds__(1024) gated_norm_add_kernel(
     }
 }
 
-// gate may be null (no gate); ring may be null (nothing to file).  y_splits 0: y is [n_tokens, width] of `dtype`.
+// gate may be null (no gate); ring may be null (nothing to file).  y_splits 0: y is [n_tokens, width] of `dtype`;
+// the gate likewise with g_splits.
 FL_API int fl_gated_norm_add(float* x, long x_ld, const void* y, long y_ld, int y_splits, long y_split_stride,
-                             const void* gate, long gate_ld, int dtype, const float* gate_bias, const float* w, float eps,
+                             const void* gate, long gate_ld, int g_splits, long g_split_stride, int dtype,
+                             const float* gate_bias, const float* w, float eps,
                              int n_tokens, int width, float* ring, long ring_slot_stride, int taps, const int* positions,
                              const int* tok_req, const int* req_start, const int* req_qlen, const int* req_slot,
                              cudaStream_t stream) {
@@ -204,9 +228,9 @@ FL_API int fl_gated_norm_add(float* x, long x_ld, const void* y, long y_ld, int 
     FL_DISPATCH(dtype, TD, {
         // four channels a thread where every row takes 16-byte (8-byte for bfloat16) accesses; which form runs, and
         // with how many threads, depends on the layer's width and buffers only, never on the step
-        const int y_bytes = y_splits > 0 ? 4 : (int)sizeof(TD);
+        const int y_bytes = y_splits > 0 ? 4 : (int)sizeof(TD), g_bytes = g_splits > 0 ? 4 : (int)sizeof(TD);
         const bool vec = width % 4 == 0 && fl_rows_take_vectors(x, x_ld, 4) && fl_rows_take_vectors(y, y_ld, y_bytes) &&
-                         y_split_stride % 4 == 0 && fl_rows_take_vectors(gate, gate_ld, sizeof(TD)) &&
+                         y_split_stride % 4 == 0 && g_split_stride % 4 == 0 && fl_rows_take_vectors(gate, gate_ld, g_bytes) &&
                          fl_rows_take_vectors(ring, ring_slot_stride, 4) && fl_rows_take_vectors(w, 4, 4) &&
                          fl_rows_take_vectors(gate_bias, 4, 4);
         const int per_thread = vec ? 4 : 2;
@@ -218,8 +242,8 @@ FL_API int fl_gated_norm_add(float* x, long x_ld, const void* y, long y_ld, int 
             if (e != cudaSuccess) return (int)e;
         }
         return fl_launch(kernel, dim3(n_tokens), dim3(threads), smem, stream, x, x_ld, y, y_ld, y_splits, y_split_stride,
-                         (const TD*)gate, gate_ld, gate_bias, w, eps, width, ring, ring_slot_stride, taps, positions,
-                         tok_req, req_start, req_qlen, req_slot);
+                         gate, gate_ld, g_splits, g_split_stride, gate_bias, w, eps, width, ring, ring_slot_stride, taps,
+                         positions, tok_req, req_start, req_qlen, req_slot);
     });
     return 0;
 }

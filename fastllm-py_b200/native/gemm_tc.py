@@ -81,12 +81,13 @@ def plan(m: int, n: int, k: int, num_sms: int, deferred: bool = False):
 
 
 SCRATCH = "split-K partial sums"
+SIDE_SCRATCH = "split-K partial sums (side)"    # a second buffer: one product's sums may wait there while others run
 
 
-def _workspace(device, floats: int) -> torch.Tensor:
+def _workspace(device, floats: int, side: bool = False) -> torch.Tensor:
     """Float scratch for split-K partial sums (see `scratch`: grows on demand, never inside
     a graph capture, and a growth invalidates captured graphs)."""
-    return scratch.get(device, SCRATCH, floats, at_least=4 << 20)
+    return scratch.get(device, SIDE_SCRATCH if side else SCRATCH, floats, at_least=(1 << 20) if side else (4 << 20))
 
 
 def workspace_floats(m: int, n: int, k: int, device) -> int:
@@ -99,14 +100,14 @@ def workspace_floats(m: int, n: int, k: int, device) -> int:
     return need
 
 
-def reserve(device, n: int, k: int, max_tokens: int) -> None:
+def reserve(device, n: int, k: int, max_tokens: int, side: bool = False) -> None:
     """Size the scratch for every step of up to `max_tokens` tokens of an [n, k] weight.  Up to
     1024 tokens the plan weighs candidates by a cost model, so every count is asked; above that
     the splits depend on the number of token tiles only, and within a bracket of 64 tokens the
     largest need is at the bracket's top."""
     counts = list(range(1, min(1024, max_tokens) + 1)) + list(range(1088, max_tokens + 64, 64))
     need = max(workspace_floats(min(m, max_tokens), n, k, device) for m in counts)
-    scratch.reserve(device, SCRATCH, need)
+    scratch.reserve(device, SIDE_SCRATCH if side else SCRATCH, need)
 
 
 class PackedWeight:
@@ -150,14 +151,15 @@ class Partial:
     them.  The workspace is reused by the next split-K product, so a Partial must
     be consumed before that; `check()` raises if it was not."""
 
-    def __init__(self, data, splits, rows, cols, ld, device):
+    def __init__(self, data, splits, rows, cols, ld, device, side: bool = False):
         self.data, self.splits, self.rows, self.cols, self.ld = data, splits, rows, cols, ld
         self.split_stride = rows * ld
         self.device = device
-        self.serial = _state.get(("serial", device), 0)
+        self.serial_key = ("serial", device, "side") if side else ("serial", device)
+        self.serial = _state.get(self.serial_key, 0)
 
     def check(self):
-        if self.serial != _state.get(("serial", self.device), 0):
+        if self.serial != _state.get(self.serial_key, 0):
             raise RuntimeError("split-K partial sums were overwritten by a later product before use")
 
     def reduce_into(self, out: torch.Tensor) -> torch.Tensor:
@@ -194,26 +196,27 @@ def _remember(key, launch) -> None:
 
 
 def gemm(a: torch.Tensor, w, out: torch.Tensor, bn: int = 0, splits: int = 0,
-         defer: bool = False):
+         defer: bool = False, side: bool = False):
     """out[M, N] = a[M, K] @ w[N, K]^T; a and w bfloat16 (row pitch a multiple of 8
     elements, base 16-byte aligned; w may be a PackedWeight), out bfloat16 or float32.
 
     With `defer`, a product whose K is split returns a Partial instead of
-    writing `out`: its consumer adds the slabs while it reads them."""
+    writing `out`: its consumer adds the slabs while it reads them.  With `side`
+    the slabs lie in the second scratch buffer, where later products of the
+    first buffer do not overwrite them."""
     # A product asked for again with the same operands in the same places (a layer's buffers do not move
     # from step to step) is launched from what the first call worked out: the checks, the plan and the
     # argument conversions below cost more host time than the driver's launch.
     _forget_if_scratch_moved(a.device)
     key = (a.data_ptr(), a.shape, a.stride(0), a.dtype, w.data_ptr(), w.shape, out.data_ptr(), out.shape,
-           out.stride(0), out.dtype, bn, splits, defer)
+           out.stride(0), out.dtype, bn, splits, defer, side)
     known = _launches.get(key)
+    serial_key = ("serial", a.device, "side") if side else ("serial", a.device)
     if known is not None:
         fn, args, kernels, partial = known
         if partial is not None:
-            serial_key = ("serial", a.device)
             partial.serial = _state[serial_key] = _state.get(serial_key, 0) + 1
         elif kernels == 2:
-            serial_key = ("serial", a.device)
             _state[serial_key] = _state.get(serial_key, 0) + 1
         ops._check(fn(*args, ops._stream()), "gemm_tcgen05", kernels)
         return partial
@@ -236,18 +239,17 @@ def gemm(a: torch.Tensor, w, out: torch.Tensor, bn: int = 0, splits: int = 0,
     ws, ws_floats = None, 0
     if splits > 1:
         ws_floats = splits * m * (-(-n // 4) * 4)
-        ws = _workspace(a.device, ws_floats)
+        ws = _workspace(a.device, ws_floats, side)
         ws_floats = ws.numel()
     deferred = defer and splits > 1
     fn = _lib().fl_gemm_tc_partial if deferred else _lib().fl_gemm_tc
     if splits > 1:
-        serial_key = ("serial", a.device)
         _state[serial_key] = _state.get(serial_key, 0) + 1    # earlier Partials are now stale
     args = (ops._ptr(a), lda, w_ptr, ldw, ops._ptr(out), ops.dtype_code(out), ldc,
             m, n, k, bn, splits, ops._ptr(ws), ws_floats, sms, ops._ptr(status_word(a.device)))
     kernels = 2 if (splits > 1 and not deferred) else 1
     ops._check(fn(*args, ops._stream()), "gemm_tcgen05", kernels)
-    partial = Partial(ws, splits, m, n, -(-n // 4) * 4, a.device) if deferred else None
+    partial = Partial(ws, splits, m, n, -(-n // 4) * 4, a.device, side) if deferred else None
     _remember(key, (fn, args, kernels, partial))
     return partial
 
@@ -358,5 +360,5 @@ class TensorCoreLinear:
             weight = padded[:, :k]
         self.weight = weight
 
-    def forward(self, a: torch.Tensor, out: torch.Tensor, defer: bool = False):
-        return gemm(a, self.weight, out, defer=defer)
+    def forward(self, a: torch.Tensor, out: torch.Tensor, defer: bool = False, side: bool = False):
+        return gemm(a, self.weight, out, defer=defer, side=side)

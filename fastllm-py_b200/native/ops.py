@@ -610,28 +610,35 @@ def input_conv(x, w, taps, ring, step, h, hc):
               _ld(hc), dtype_code(hc), x.shape[0], x.shape[1], _stream()), "input_conv")
 
 
-def gated_norm_add(x, y, gate, gate_bias, w, eps, step, ring=None, taps=1):
-    """x += rmsnorm(y * sigmoid(gate + gate_bias)) * w (no gate: rmsnorm(y) * w).  y is a matrix, or a product left as
-    split-K partial sums (`gemm_tc.Partial`), which the kernel adds up as it reads them and rounds to `gate`'s dtype.
-    With `ring`, the rows of x as they were before the add are filed for the request's last taps - 1 rows of the step
-    (see `input_conv`)."""
-    partial = not isinstance(y, torch.Tensor)
-    if partial:
-        y.check()
-        if gate is None or (y.rows, y.cols) != tuple(x.shape):
-            raise KernelError("gated_norm_add: partial sums need a gate (it names the dtype) and the stream's shape")
-        y_data, y_ld, y_splits, y_stride, code = y.data, y.ld, y.splits, y.split_stride, dtype_code(gate)
-    else:
-        y_data, y_ld, y_splits, y_stride, code = y, _ld(y), 0, 0, dtype_code(y)
-    _require_cuda(x, y_data, gate, gate_bias, w, ring)
-    if x.dtype != torch.float32 or w.dtype != torch.float32 or (gate is not None and not partial and gate.dtype != y.dtype) \
-            or (gate_bias is not None and gate_bias.dtype != torch.float32):
-        raise KernelError("gated_norm_add: float32 stream, weights and bias; gate of the sublayer output's dtype")
+def gated_norm_add(x, y, gate, gate_bias, w, eps, step, ring=None, taps=1, dtype=None):
+    """x += rmsnorm(y * sigmoid(gate + gate_bias)) * w (no gate: rmsnorm(y) * w).  y and gate are matrices of one
+    dtype, or products left as split-K partial sums (`gemm_tc.Partial`), which the kernel adds up as it reads them
+    and rounds to `dtype` (the type the matrix would have had; needed when neither is a matrix).  With `ring`, the
+    rows of x as they were before the add are filed for the request's last taps - 1 rows of the step (see
+    `input_conv`)."""
+    def operand(v):
+        if v is None:
+            return None, 0, 0, 0, None
+        if isinstance(v, torch.Tensor):
+            return v, _ld(v), 0, 0, v.dtype
+        v.check()
+        if (v.rows, v.cols) != tuple(x.shape):
+            raise KernelError("gated_norm_add: partial sums must have the stream's shape")
+        return v.data, v.ld, v.splits, v.split_stride, None
+
+    y_data, y_ld, y_splits, y_stride, y_dt = operand(y)
+    g_data, g_ld, g_splits, g_stride, g_dt = operand(gate)
+    dt = y_dt or g_dt or dtype
+    if dt is None or (y_dt or dt) != dt or (g_dt or dt) != dt:
+        raise KernelError("gated_norm_add: the sublayer's result and the gate share one dtype (name it for partial sums)")
+    _require_cuda(x, y_data, g_data, gate_bias, w, ring)
+    if x.dtype != torch.float32 or w.dtype != torch.float32 or (gate_bias is not None and gate_bias.dtype != torch.float32):
+        raise KernelError("gated_norm_add: float32 stream, weights and bias")
     fn = _fn("gated_block", "fl_gated_norm_add", [c_void_p, c_long, c_void_p, c_long, c_int, c_long, c_void_p, c_long, c_int,
-                                                  c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_long, c_int,
-                                                  c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
-    _check(fn(_ptr(x), _ld(x), _ptr(y_data), y_ld, y_splits, y_stride, _ptr(gate), 0 if gate is None else _ld(gate), code,
-              _ptr(gate_bias), _ptr(w), float(eps), x.shape[0], x.shape[1], _ptr(ring),
+                                                  c_long, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_long,
+                                                  c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(x), _ld(x), _ptr(y_data), y_ld, y_splits, y_stride, _ptr(g_data), g_ld, g_splits, g_stride,
+              _CODES[dt], _ptr(gate_bias), _ptr(w), float(eps), x.shape[0], x.shape[1], _ptr(ring),
               0 if ring is None else ring.stride(0), int(taps), _ptr(step.positions), _ptr(step.tok_req),
               _ptr(step.req_start), _ptr(step.req_qlen), _ptr(step.req_slot), _stream()), "gated_norm_add")
 

@@ -204,7 +204,7 @@ class GatedPostNormBlock(Part):
 
     def reserve(self, limits):
         for lin in self.gate.values():
-            lin.reserve(self.ctx.dtype, limits.max_tokens)
+            lin.reserve(self.ctx.dtype, limits.max_tokens, side=True)
 
     def _out_weight(self, s, norm):
         w = self._w_out.get(s)
@@ -226,15 +226,15 @@ class GatedPostNormBlock(Part):
         hc = ws.rows("conv_in", n, self.hidden, dt)
         ops.input_conv(stream.x, self.conv[s], taps, ring, step, h, hc)
         gate = None
-        if self.gated:                                        # before the sublayer: its last product may then stay
-            gate = ws.rows("branch_gate", n, self.hidden, dt)  # split-K partial sums until the kernel below adds them
-            self.gate[s].forward(h, gate)
+        if self.gated:
+            # before the sublayer, into the second scratch buffer: both this product and the sublayer's last one may
+            # then stay split-K partial sums until the kernel below adds them up
+            gate = ws.rows("branch_gate", n, self.hidden, dt)
+            gate = self.gate[s].forward(h, gate, defer=True, side=True) or gate
         delta = ws.rows("delta", n, self.hidden, dt)
         left = run(hc, delta)
-        if left is not None and not self.gated:
-            left = left.reduce_into(delta)
         ops.gated_norm_add(stream.x, delta if left is None else left, gate, self.gate_bias.get(s),
-                           self._out_weight(s, norm), norm.eps, step, ring, taps)
+                           self._out_weight(s, norm), norm.eps, step, ring, taps, dtype=dt)
 
     def forward(self, stream, step, cache, state=None):
         stream.settle()                                       # the sublayers read x itself

@@ -56,12 +56,14 @@ class Linear:
         self.out_features, self.in_features = w.shape
         self.dtype, self.device = w.dtype, w.device
 
-    def forward(self, a: torch.Tensor, out: torch.Tensor, defer: bool = False):
+    def forward(self, a: torch.Tensor, out: torch.Tensor, defer: bool = False, side: bool = False):
         """Writes `out` and returns None; or, with `defer`, may leave the product
         as split-K partial sums and return them (a `gemm_tc.Partial`) for a
-        consumer that adds them as it reads: `out` is then not written."""
+        consumer that adds them as it reads: `out` is then not written.  `side`:
+        the partial sums go to the second scratch buffer (reserve with `side` too),
+        where they outlive the products that follow in the first."""
         if a.dtype == torch.bfloat16 and self.dtype == torch.bfloat16:
-            return self._tensor_core().forward(a, out, defer)
+            return self._tensor_core().forward(a, out, defer, side)
         if self.weight is None:
             raise ops.KernelError("this Linear's matrix was packed for bfloat16 activations; it cannot "
                                   "serve 32-bit activations as well")
@@ -76,7 +78,7 @@ class Linear:
                 self.weight = None             # the packed copy is the matrix from here on
         return self._tc
 
-    def reserve(self, activation_dtype, max_tokens: int) -> None:
+    def reserve(self, activation_dtype, max_tokens: int, side: bool = False) -> None:
         """Called when an engine is built: make the matrix ready for the kernels that will read it
         (pack it, for bfloat16 products) and size the scratch memory that products of up to
         `max_tokens` rows will take, so that nothing has to grow (and no captured graph goes
@@ -84,7 +86,7 @@ class Linear:
         if activation_dtype == torch.bfloat16 and self.dtype == torch.bfloat16:
             from ..native import gemm_tc
             self._tensor_core()
-            gemm_tc.reserve(self.device, self.out_features, self.in_features, max_tokens)
+            gemm_tc.reserve(self.device, self.out_features, self.in_features, max_tokens, side)
 
     def forward_qkv_rope(self, a: torch.Tensor, q_out: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int,
                          rot_dim: int, cos, sin, positions, slots, cache, page_size: int) -> bool:

@@ -559,7 +559,9 @@ def test_gated_norm_add_adds_up_partial_sums_like_the_reduce_kernel(dtype, width
     gen = torch.Generator().manual_seed(9)
     n, splits, ld = 5, 3, -(-width // 4) * 4
     slabs = torch.randn(splits, n, ld, generator=gen).cuda()
-    gate = torch.randn(n, width, generator=gen).cuda().to(dtype)
+    gate_slabs = torch.randn(2, n, ld, generator=gen).cuda()
+    gate_part = Partial(gate_slabs, 2, n, width, ld, slabs.device, side=True)
+    gate = gate_part.reduce_into(torch.empty(n, width, device="cuda", dtype=dtype))
     bias, w = torch.randn(width, generator=gen).cuda(), torch.randn(width, generator=gen).cuda()
     dev = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
     step = SimpleNamespace(positions=dev(list(range(n))), tok_req=dev([0] * n), req_start=dev([0, n]), req_qlen=dev([n]),
@@ -568,10 +570,11 @@ def test_gated_norm_add_adds_up_partial_sums_like_the_reduce_kernel(dtype, width
     part = Partial(slabs, splits, n, width, ld, slabs.device)
     y = torch.empty(n, width, device="cuda", dtype=dtype)
     part.reduce_into(y)
-    a, b = x0.clone(), x0.clone()
+    a, b, c = x0.clone(), x0.clone(), x0.clone()
     ops.gated_norm_add(a, y, gate, bias, w, 1e-6, step)
     ops.gated_norm_add(b, part, gate, bias, w, 1e-6, step)
-    assert torch.equal(a, b)
+    ops.gated_norm_add(c, part, gate_part, bias, w, 1e-6, step, dtype=dtype)
+    assert torch.equal(a, b) and torch.equal(a, c)
     z = slabs.double().sum(0)[:, :width].to(dtype).double() * torch.sigmoid(gate.double() + bias.double())
     want = x0.double() + z / torch.sqrt((z * z).mean(-1, keepdim=True) + 1e-6) * w.double()
     assert torch.allclose(a.double(), want, atol=2e-5 if dtype == torch.float32 else 2e-2)

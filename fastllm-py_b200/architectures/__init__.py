@@ -1,2 +1,2 @@
 """Importing this package registers the architectures the engine ships with."""
-from . import lasonex, llama, sakusun, tigitar  # noqa: F401
+from . import lasonex, llama, saberax, sakusun, tigitar  # noqa: F401

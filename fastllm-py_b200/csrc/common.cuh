@@ -77,7 +77,10 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 // `act` selects f, the same in every thread of a launch:
 //   0 silu(g) * u      1 relu(g) * u      2 gelu(g) * u in its tanh form
 //   3 the clamped swish unit: g' = min(g, p0), u' = clamp(u, -p0, p0), g' * sigmoid(p1 g') * (u' + 1)
-enum FlAct : int { FL_ACT_SILU = 0, FL_ACT_RELU = 1, FL_ACT_GELU_TANH = 2, FL_ACT_CLAMPED_SWISH = 3, FL_ACT_COUNT = 4 };
+//   4 relu(g)^2 * u
+// A unit without a gate is f(x, 1).
+enum FlAct : int { FL_ACT_SILU = 0, FL_ACT_RELU = 1, FL_ACT_GELU_TANH = 2, FL_ACT_CLAMPED_SWISH = 3, FL_ACT_RELU_SQUARED = 4,
+                   FL_ACT_COUNT = 5 };
 struct FlGate {
     int act;
     float p0, p1;
@@ -85,6 +88,7 @@ struct FlGate {
 
 __device__ __forceinline__ float fl_gated(float g, float u, const FlGate a) {
     if (a.act == FL_ACT_RELU) return fmaxf(g, 0.0f) * u;
+    if (a.act == FL_ACT_RELU_SQUARED) return fmaxf(g, 0.0f) * fmaxf(g, 0.0f) * u;
     if (a.act == FL_ACT_GELU_TANH) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
     if (a.act == FL_ACT_CLAMPED_SWISH) {
         g = fminf(g, a.p0);

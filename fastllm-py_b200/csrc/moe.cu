@@ -5,11 +5,14 @@
 //                 s = sigmoid(z) (or a softmax over the experts); the `top` experts with the largest
 //                 s + bias are chosen (the bias steers the choice only), ties to the lower index; the
 //                 weights are the chosen s, optionally renormalised to sum 1 (divided by their sum + an
-//                 epsilon).  With groups, the experts form `n_groups` equal groups of neighbours, a
-//                 group's score is the largest s + bias in it, and only experts of the `keep` best
-//                 groups (ties to the lower index) can be chosen
-//   moe_gate_up   per (token, choice): act(W_gate[e] h) * (W_up[e] h), one warp per feature
-//   moe_down      per token: sum over its choices, in order of choice, of weight * W_down[e] a
+//                 epsilon) and multiplied by `weight_scale`.  With groups, the experts form `n_groups`
+//                 equal groups of neighbours, a group's score is the sum of the `group_top` largest
+//                 s + bias in it (1: the largest), and only experts of the `keep` best groups (ties to
+//                 the lower index) can be chosen
+//   moe_gate_up   per (token, choice): act(W_gate[e] h) * (W_up[e] h), one warp per feature; experts
+//                 without a gate: act(W_up[e] h), the unit's f(x, 1)
+//   moe_down      per token: sum over its choices, in order of choice, of weight * W_down[e] a (with
+//                 `accumulate` added to what `out` holds: a shared unit's result)
 //
 // The last two read an expert's matrices once per token that chose it: the right shape for decode
 // steps, where tokens are few and the matrices stream from memory.  All sums are float and depend only
@@ -21,7 +24,8 @@ template <typename TW>
 __global__ void __launch_bounds__(128) moe_pick_kernel(const float* __restrict__ z, long z_ld, const TW* __restrict__ bias,
                                                        int* __restrict__ chosen, float* __restrict__ weights, int n_tokens,
                                                        int experts, int top, int softmax_scores, int renormalise,
-                                                       int n_groups, int keep, float renorm_eps) {
+                                                       int n_groups, int keep, float renorm_eps, int group_top,
+                                                       float weight_scale) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float route_s[];                  // per warp: [experts] scores, [experts] scores + bias, [n_groups]
@@ -48,8 +52,20 @@ __global__ void __launch_bounds__(128) moe_pick_kernel(const float* __restrict__
         const int per = experts / n_groups;
         float* group = pick + experts;
         for (int g = lane; g < n_groups; g += 32) {
-            float b = -CUDART_INF_F;
-            for (int i = 0; i < per; ++i) b = fmaxf(b, pick[g * per + i]);
+            float b = 0.0f, last = CUDART_INF_F;        // the sum of the group's `group_top` largest, in falling order
+            int last_at = -1;
+            for (int n = 0; n < group_top && n < per; ++n) {
+                float best = -CUDART_INF_F;
+                int at = per;
+                for (int i = 0; i < per; ++i) {
+                    const float v = pick[g * per + i];
+                    if ((v < last || (v == last && i > last_at)) && v > best) { best = v; at = i; }
+                }
+                if (at == per) break;
+                b += best;
+                last = best;
+                last_at = at;
+            }
             group[g] = b;
         }
         __syncwarp();
@@ -82,15 +98,20 @@ __global__ void __launch_bounds__(128) moe_pick_kernel(const float* __restrict__
         total += score[at];
         __syncwarp();
     }
-    if (renormalise && lane == 0)
-        for (int k = 0; k < top; ++k) weights[(long)t * top + k] /= total + renorm_eps;
+    if (lane == 0)
+        for (int k = 0; k < top; ++k) {
+            float w = weights[(long)t * top + k];
+            if (renormalise) w /= total + renorm_eps;
+            weights[(long)t * top + k] = w * weight_scale;
+        }
 }
 
-// w_gu: [experts][2 ff][width] (gate rows, then up rows); a: [tokens x top][ff] float
+// w_gu: [experts][2 ff][width] (gate rows, then up rows), or [experts][ff][width] without a gate;
+// a: [tokens x top][ff] float
 template <typename T, typename TW>
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T* __restrict__ h, long h_ld, const TW* __restrict__ w_gu,
                                                           const int* __restrict__ chosen, float* __restrict__ a,
-                                                          int width, int ff, int top, FlGate act) {
+                                                          int width, int ff, int top, FlGate act, int gated) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float moe_x[];                    // [width]
@@ -100,6 +121,14 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T* __restrict__ 
     __syncthreads();
     const int f = blockIdx.y * 8 + warp;
     if (f >= ff) return;
+    if (!gated) {
+        const TW* wx = w_gu + ((long)chosen[pair] * ff + f) * width;
+        float x = 0.0f;
+        for (int i = lane; i < width; i += 32) x += moe_x[i] * to_f32<TW>(wx[i]);
+        x = warp_sum(x);
+        if (lane == 0) a[(long)pair * ff + f] = fl_gated(x, 1.0f, act);
+        return;
+    }
     const TW* wg = w_gu + ((long)chosen[pair] * 2 * ff + f) * width;
     const TW* wu = wg + (long)ff * width;
     float g = 0.0f, u = 0.0f;
@@ -116,7 +145,8 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const T* __restrict__ 
 template <typename T, typename TW>
 __global__ void __launch_bounds__(256) moe_down_kernel(const float* __restrict__ a, const TW* __restrict__ w_down,
                                                        const int* __restrict__ chosen, const float* __restrict__ weights,
-                                                       T* __restrict__ out, long out_ld, int width, int ff, int top) {
+                                                       T* __restrict__ out, long out_ld, int width, int ff, int top,
+                                                       int accumulate) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -131,28 +161,29 @@ __global__ void __launch_bounds__(256) moe_down_kernel(const float* __restrict__
         for (int i = lane; i < ff; i += 32) y += ar[i] * to_f32<TW>(wd[i]);
         sum += weights[pair] * warp_sum(y);
     }
-    if (lane == 0) out[(long)t * out_ld + c] = from_f32<T>(sum);
+    if (lane == 0) out[(long)t * out_ld + c] = from_f32<T>(accumulate ? to_f32<T>(out[(long)t * out_ld + c]) + sum : sum);
 }
 
 FL_API int fl_moe_pick(const float* z, long z_ld, const void* bias, int bias_dtype, int* chosen, float* weights,
                        int n_tokens, int experts, int top, int softmax_scores, int renormalise, int n_groups, int keep,
-                       float renorm_eps, cudaStream_t stream) {
+                       float renorm_eps, int group_top, float weight_scale, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_groups < 1) n_groups = keep = 1;
     const size_t smem = (size_t)(2 * experts + n_groups) * 4 * sizeof(float);
     if (top < 1 || top > experts || smem > 48 * 1024 || experts % n_groups || keep < 1 || keep > n_groups ||
-        (long)keep * (experts / n_groups) < top)
+        (long)keep * (experts / n_groups) < top || group_top < 1)
         return (int)cudaErrorInvalidValue;
     FL_DISPATCH(bias_dtype, TW,
         return fl_launch(moe_pick_kernel<TW>, dim3((n_tokens + 3) / 4), dim3(128), smem, stream,
                          z, z_ld, (const TW*)bias, chosen, weights, n_tokens, experts, top, softmax_scores, renormalise,
-                         n_groups, keep, renorm_eps));
+                         n_groups, keep, renorm_eps, group_top, weight_scale));
     return 0;
 }
 
 FL_API int fl_moe_experts(const void* h, int dtype, long h_ld, const void* w_gu, const void* w_down, int w_dtype,
                           const int* chosen, const float* weights, float* a, void* out, long out_ld, int n_tokens,
-                          int width, int ff, int top, int act, float act_p0, float act_p1, cudaStream_t stream) {
+                          int width, int ff, int top, int act, float act_p0, float act_p1, int gated,
+                          int accumulate, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if ((size_t)width * sizeof(float) > 48 * 1024 || (ff + 7) / 8 > 65535 || (width + 7) / 8 > 65535 || act < 0 || act >= FL_ACT_COUNT)
         return (int)cudaErrorInvalidValue;
@@ -160,11 +191,11 @@ FL_API int fl_moe_experts(const void* h, int dtype, long h_ld, const void* w_gu,
     FL_DISPATCH(dtype, T, FL_DISPATCH(w_dtype, TW,
         rc = fl_launch(moe_gate_up_kernel<T, TW>, dim3(n_tokens * top, (ff + 7) / 8), dim3(256),
                        (size_t)width * sizeof(float), stream, (const T*)h, h_ld, (const TW*)w_gu, chosen, a, width, ff,
-                       top, FlGate{act, act_p0, act_p1})));
+                       top, FlGate{act, act_p0, act_p1}, gated)));
     if (rc) return rc;
     FL_DISPATCH(dtype, T, FL_DISPATCH(w_dtype, TW,
         return fl_launch(moe_down_kernel<T, TW>, dim3(n_tokens, (width + 7) / 8), dim3(256), 0, stream, (const float*)a,
-                         (const TW*)w_down, chosen, weights, (T*)out, out_ld, width, ff, top)));
+                         (const TW*)w_down, chosen, weights, (T*)out, out_ld, width, ff, top, accumulate)));
     return 0;
 }
 
@@ -177,7 +208,8 @@ FL_API int fl_moe_experts(const void* h, int dtype, long h_ld, const void* w_gu,
 //   moe_group_mma   bfloat16 mma.sync m16n8k16, 64 rows x 128 weight rows per block, K in steps of 32 through
 //                   a three-stage cp.async ring.  GATED: the 128 weight rows are 64 gate rows and the 64 up rows
 //                   of the same features, A rows are gathered token rows, the epilogue writes act(g) * u
-//                   (bfloat16, in row order); else A is that buffer and the output float [rows, width]
+//                   (bfloat16, in row order); UP: experts without a gate, A gathered, 128 up rows, the epilogue
+//                   writes the unit's f(x, 1); DOWN: A is that buffer and the output float [rows, width]
 //   moe_combine     out[t] = sum_k weight[t, k] * y[row of pair (t, k)], in order of choice
 //
 // A row's sums do not depend on the other rows of its tile, so the order of rows within an expert (it
@@ -236,13 +268,15 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 #define MOE_SMEM (MOE_STAGES * (MOE_TM + 128) * MOE_PITCH * 2)
 
 // grid: (tiles of rows, blocks of 64 features (GATED) or 128 columns).  K % 32 == 0, rows 16-byte aligned.
-template <bool GATED>
+enum { MOE_DOWN = 0, MOE_GATED = 1, MOE_UP = 2 };
+template <int MODE>
 __global__ void __launch_bounds__(256) moe_group_mma_kernel(
     const bf16* __restrict__ a, long a_ld, const bf16* __restrict__ w, int n_out, int K, const int* __restrict__ row_pair,
     const int* __restrict__ tile_expert, const int* __restrict__ n_tiles, int top, bf16* __restrict__ act_out,
     float* __restrict__ y_out, long out_ld, FlGate act) {
     pdl_wait();
     pdl_trigger();
+    constexpr bool GATED = MODE == MOE_GATED;
     extern __shared__ __align__(16) unsigned char moe_smem[];
     bf16 (*a_s)[MOE_TM][MOE_PITCH] = reinterpret_cast<bf16 (*)[MOE_TM][MOE_PITCH]>(moe_smem);
     bf16 (*w_s)[128][MOE_PITCH] = reinterpret_cast<bf16 (*)[128][MOE_PITCH]>(moe_smem + MOE_STAGES * MOE_TM * MOE_PITCH * 2);
@@ -257,7 +291,7 @@ __global__ void __launch_bounds__(256) moe_group_mma_kernel(
     // sources of this thread's 16-byte pieces of a stage: its part of one row of A and of two rows of W
     const int ar = tid >> 2, ac = (tid & 3) * 8 * MOE_PIECES;
     const bf16* a_src;
-    if (GATED) {
+    if (MODE != MOE_DOWN) {
         const int pair = pair_s[ar];
         a_src = a + (long)(pair < 0 ? 0 : pair / top) * a_ld + ac;
     } else {
@@ -355,7 +389,9 @@ __global__ void __launch_bounds__(256) moe_group_mma_kernel(
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         const int col = blockIdx.y * 128 + wn * 32 + j * 8 + (lane & 3) * 2 + c;
-                        if (col < n_out) y_out[row * out_ld + col] = acc[i][j][half * 2 + c];
+                        if (col >= n_out) continue;
+                        if (MODE == MOE_UP) act_out[row * out_ld + col] = __float2bfloat16_rn(fl_gated(acc[i][j][half * 2 + c], 1.0f, act));
+                        else y_out[row * out_ld + col] = acc[i][j][half * 2 + c];
                     }
             }
         }
@@ -364,14 +400,14 @@ __global__ void __launch_bounds__(256) moe_group_mma_kernel(
 template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, long y_ld, const int* __restrict__ pair_row,
                                                           const float* __restrict__ weights, T* __restrict__ out, long out_ld,
-                                                          int width, int top) {
+                                                          int width, int top, int accumulate) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
         float sum = 0.0f;
         for (int k = 0; k < top; ++k) sum += weights[(long)t * top + k] * y[(long)pair_row[(long)t * top + k] * y_ld + c];
-        out[(long)t * out_ld + c] = from_f32<T>(sum);
+        out[(long)t * out_ld + c] = from_f32<T>(accumulate ? to_f32<T>(out[(long)t * out_ld + c]) + sum : sum);
     }
 }
 
@@ -388,9 +424,11 @@ FL_API int fl_moe_group_takes(int dtype, int w_dtype, int width, int ff) {
 static int moe_group_smem_ready() {
     static int rc = -1;
     if (rc < 0) {
-        rc = (int)cudaFuncSetAttribute(moe_group_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, MOE_SMEM);
+        rc = (int)cudaFuncSetAttribute(moe_group_mma_kernel<MOE_GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, MOE_SMEM);
         if (rc == 0)
-            rc = (int)cudaFuncSetAttribute(moe_group_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, MOE_SMEM);
+            rc = (int)cudaFuncSetAttribute(moe_group_mma_kernel<MOE_DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, MOE_SMEM);
+        if (rc == 0)
+            rc = (int)cudaFuncSetAttribute(moe_group_mma_kernel<MOE_UP>, cudaFuncAttributeMaxDynamicSharedMemorySize, MOE_SMEM);
     }
     return rc;
 }
@@ -400,7 +438,7 @@ static int moe_group_smem_ready() {
 FL_API int fl_moe_experts_grouped(const void* h, long h_ld, const void* w_gu, const void* w_down, const int* chosen,
                                   const float* weights, int* ints, void* act, float* y, void* out, long out_ld,
                                   int n_tokens, int width, int ff, int top, int experts, int act_code, float act_p0, float act_p1,
-                                  cudaStream_t stream) {
+                                  int gated, int accumulate, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (act_code < 0 || act_code >= FL_ACT_COUNT) return (int)cudaErrorInvalidValue;
     const FlGate gate{act_code, act_p0, act_p1};
@@ -416,16 +454,21 @@ FL_API int fl_moe_experts_grouped(const void* h, long h_ld, const void* w_gu, co
     rc = fl_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)(2 * experts + 1) * sizeof(int), stream, chosen,
                        n_tokens * top, experts, row_pair, pair_row, tile_expert, n_tiles, max_tiles);
     if (rc) return rc;
-    rc = fl_launch(moe_group_mma_kernel<true>, dim3(max_tiles, (ff + 63) / 64), dim3(256), MOE_SMEM, stream, (const bf16*)h, h_ld,
-                   (const bf16*)w_gu, ff, width, (const int*)row_pair, (const int*)tile_expert, (const int*)n_tiles, top,
-                   (bf16*)act, (float*)nullptr, (long)ff, gate);
+    if (gated)
+        rc = fl_launch(moe_group_mma_kernel<MOE_GATED>, dim3(max_tiles, (ff + 63) / 64), dim3(256), MOE_SMEM, stream, (const bf16*)h, h_ld,
+                       (const bf16*)w_gu, ff, width, (const int*)row_pair, (const int*)tile_expert, (const int*)n_tiles, top,
+                       (bf16*)act, (float*)nullptr, (long)ff, gate);
+    else
+        rc = fl_launch(moe_group_mma_kernel<MOE_UP>, dim3(max_tiles, (ff + 127) / 128), dim3(256), MOE_SMEM, stream, (const bf16*)h, h_ld,
+                       (const bf16*)w_gu, ff, width, (const int*)row_pair, (const int*)tile_expert, (const int*)n_tiles, top,
+                       (bf16*)act, (float*)nullptr, (long)ff, gate);
     if (rc) return rc;
-    rc = fl_launch(moe_group_mma_kernel<false>, dim3(max_tiles, (width + 127) / 128), dim3(256), MOE_SMEM, stream,
+    rc = fl_launch(moe_group_mma_kernel<MOE_DOWN>, dim3(max_tiles, (width + 127) / 128), dim3(256), MOE_SMEM, stream,
                    (const bf16*)act, (long)ff, (const bf16*)w_down, width, ff, (const int*)row_pair,
                    (const int*)tile_expert, (const int*)n_tiles, top, (bf16*)nullptr, y, (long)width, gate);
     if (rc) return rc;
     int col_blocks = (width + 255) / 256;
     if (col_blocks > 8) col_blocks = 8;
     return fl_launch(moe_combine_kernel<bf16>, dim3(n_tokens, col_blocks), dim3(256), 0, stream, (const float*)y,
-                     (long)width, (const int*)pair_row, weights, (bf16*)out, out_ld, width, top);
+                     (long)width, (const int*)pair_row, weights, (bf16*)out, out_ld, width, top, accumulate);
 }

@@ -1,0 +1,166 @@
+// A gated linear recurrence per channel (the real-gated linear recurrent unit) between two branches.
+//
+// Per token, from one product proj = [y_pre | x_pre] (each `width` wide; biases added here):
+//     y = gelu_tanh(y_pre)                                   the gate branch
+//     u = conv(x_pre)                                        causal, per channel, `taps` taps, the last tap the token's own;
+//                                                            zeros before the sequence's start
+//     r = sigmoid(A_b u_b + a_b),  i = sigmoid(I_b u_b + i_b)   per block b of width / blocks channels (square matrices)
+//     a = exp(rate * r)            rate[c] = -c softplus(lam[c]), made by the caller
+//     S <- a S + sqrt(1 - a^2) * i * u;     out = S * y
+// A request's state row is [S (width) | the last taps - 1 rows of x_pre (width each)], float; it is read unless the
+// request starts (context 0) and written at the end of the step.
+//
+//   rglru_conv    per (token, channel): u, from the step's rows of the same request and the kept rows before them
+//   rglru_gates   per (8 tokens, block): both block products on the CUDA cores in float, then a and the input term
+//   rglru_scan    per (request, channel): the recurrence over the request's tokens in order, the gate branch, the new
+//                 state and the new kept rows
+//
+// Everything after the product is float.  Every sum's order depends on the token alone.
+#include "common.cuh"
+
+#define RG_MAX_TAPS 16
+
+template <typename T>
+__global__ void __launch_bounds__(256) rglru_conv_kernel(
+    const T* __restrict__ proj, long ld, const float* __restrict__ bias, const float* __restrict__ conv_w,
+    const float* __restrict__ conv_b, const float* __restrict__ state, long state_stride, const int* __restrict__ tok_req,
+    const int* __restrict__ positions, const int* __restrict__ req_start, const int* __restrict__ req_ctx,
+    const int* __restrict__ req_slot, float* __restrict__ u, long u_ld, int width, int taps) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    const int r = tok_req[t], pos = positions[t];
+    const int start = req_start[r], ctx = req_ctx[r];
+    const float* tail = state + (long)req_slot[r] * state_stride + width;      // row k: position ctx - (taps - 1) + k
+    const float xb = bias[width + c];
+    float acc = conv_b[c];
+    for (int j = 0; j < taps; ++j) {
+        const int p = pos - (taps - 1) + j;
+        if (p < 0) continue;
+        float x;
+        if (p >= ctx) x = to_f32<T>(proj[(long)(start + p - ctx) * ld + width + c]) + xb;
+        else x = tail[(long)(p - ctx + taps - 1) * width + c];
+        acc += conv_w[(long)c * taps + j] * x;
+    }
+    u[(long)t * u_ld + c] = acc;
+}
+
+#define RG_TT 8                  // tokens of a block of rglru_gates
+
+// w_a, w_i: [blocks][bw][bw] (out, in); b_a, b_i: [blocks][bw] float.  a_out, b_out: [n, width] float.
+template <typename TW>
+__global__ void __launch_bounds__(256) rglru_gates_kernel(const float* __restrict__ u, long u_ld, const TW* __restrict__ w_a,
+                                                          const TW* __restrict__ w_i, const float* __restrict__ b_a,
+                                                          const float* __restrict__ b_i, const float* __restrict__ rate,
+                                                          float* __restrict__ a_out, float* __restrict__ b_out, long o_ld,
+                                                          int n_tokens, int width, int bw) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float u_s[];                      // [RG_TT][bw]
+    const int t0 = blockIdx.x * RG_TT, b = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_here = min(RG_TT, n_tokens - t0);
+    for (int i = threadIdx.x; i < RG_TT * bw; i += blockDim.x) {
+        const int tt = i / bw, k = i - tt * bw;
+        u_s[i] = tt < n_here ? u[(long)(t0 + tt) * u_ld + b * bw + k] : 0.0f;
+    }
+    __syncthreads();
+    for (int o = blockIdx.z * 8 + warp; o < bw; o += gridDim.z * 8) {
+        const TW* ra = w_a + ((long)b * bw + o) * bw;
+        const TW* ri = w_i + ((long)b * bw + o) * bw;
+        float sa[RG_TT], si[RG_TT];
+#pragma unroll
+        for (int tt = 0; tt < RG_TT; ++tt) sa[tt] = si[tt] = 0.0f;
+        for (int k = lane; k < bw; k += 32) {
+            const float wa = to_f32<TW>(ra[k]), wi = to_f32<TW>(ri[k]);
+#pragma unroll
+            for (int tt = 0; tt < RG_TT; ++tt) {
+                sa[tt] += wa * u_s[tt * bw + k];
+                si[tt] += wi * u_s[tt * bw + k];
+            }
+        }
+        float mine_a = 0.0f, mine_i = 0.0f;
+#pragma unroll
+        for (int tt = 0; tt < RG_TT; ++tt) {
+            const float ta = warp_sum(sa[tt]), ti = warp_sum(si[tt]);
+            if (lane == tt) { mine_a = ta; mine_i = ti; }
+        }
+        if (lane < n_here) {
+            const int c = b * bw + o;
+            const float r = 1.0f / (1.0f + expf(-(mine_a + b_a[c])));
+            const float g = 1.0f / (1.0f + expf(-(mine_i + b_i[c])));
+            const float log_a = rate[c] * r;
+            const long at = (long)(t0 + lane) * o_ld + c;
+            a_out[at] = expf(log_a);
+            b_out[at] = sqrtf(-expm1f(2.0f * log_a)) * g * u_s[lane * bw + o];
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) rglru_scan_kernel(
+    const float* __restrict__ a, const float* __restrict__ bx, long ab_ld, const T* __restrict__ proj, long ld,
+    const float* __restrict__ bias, float* __restrict__ state, long state_stride, const int* __restrict__ req_start,
+    const int* __restrict__ req_ctx, const int* __restrict__ req_qlen, const int* __restrict__ req_slot,
+    T* __restrict__ out, long out_ld, int width, int taps) {
+    pdl_wait();
+    pdl_trigger();
+    const int r = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= width) return;
+    const int start = req_start[r], ctx = req_ctx[r], qlen = req_qlen[r];
+    float* row = state + (long)req_slot[r] * state_stride;
+    float S = ctx > 0 ? row[c] : 0.0f;
+    const float yb = bias[c], xb = bias[width + c];
+#pragma unroll 4
+    for (int i = 0; i < qlen; ++i) {
+        const long t = start + i;
+        S = a[t * ab_ld + c] * S + bx[t * ab_ld + c];
+        const float z = to_f32<T>(proj[t * ld + c]) + yb;
+        const float y = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        out[t * out_ld + c] = from_f32<T>(S * y);
+    }
+    row[c] = S;
+    // the kept rows: row k is position ctx + qlen - (taps - 1) + k, from this step's rows or from the rows kept before
+    // (old row k + qlen: read at or ahead of the place being written, so the shift works in place)
+    float* tail = row + width;
+    for (int k = 0; k < taps - 1; ++k) {
+        const int p = ctx + qlen - (taps - 1) + k;
+        float x = 0.0f;
+        if (p >= ctx) x = to_f32<T>(proj[(long)(start + p - ctx) * ld + width + c]) + xb;
+        else if (p >= 0) x = tail[(long)(k + qlen) * width + c];
+        tail[(long)k * width + c] = x;
+    }
+}
+
+// proj: [n, 2 width] = y_pre | x_pre; bias: [2 width] float; conv_w: [width][taps] float; state rows:
+// width * taps floats.  u, a, bx: float [n, width] scratch.  out: [n, width] = S * y in the activations' type.
+FL_API int fl_rglru(const void* proj, int dtype, long ld, const float* bias, const float* conv_w, const float* conv_b,
+                    const void* w_a, const void* w_i, int w_dtype, const float* b_a, const float* b_i, const float* rate,
+                    float* state, long state_stride, const int* tok_req, const int* positions, const int* req_start,
+                    const int* req_ctx, const int* req_qlen, const int* req_slot, int n_tokens, int n_requests,
+                    float* u, float* a, float* bx, long s_ld, void* out, long out_ld, int width, int blocks, int taps,
+                    cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (blocks < 1 || width % blocks || taps < 1 || taps > RG_MAX_TAPS) return (int)cudaErrorInvalidValue;
+    const int bw = width / blocks;
+    const size_t smem = (size_t)RG_TT * bw * sizeof(float);
+    if (smem > 48 * 1024 || blocks > 65535) return (int)cudaErrorInvalidValue;
+    int rc = 0;
+    FL_DISPATCH(dtype, T, rc = fl_launch(rglru_conv_kernel<T>, dim3(n_tokens, (width + 255) / 256), dim3(256), 0, stream,
+                                         (const T*)proj, ld, bias, conv_w, conv_b, (const float*)state, state_stride,
+                                         tok_req, positions, req_start, req_ctx, req_slot, u, s_ld, width, taps));
+    if (rc) return rc;
+    int z = (bw + 7) / 8;                               // blocks that share a (token tile, block)'s outputs
+    const int tiles = (n_tokens + RG_TT - 1) / RG_TT;
+    while (z > 1 && (long)tiles * blocks * z > 2048) z = (z + 1) / 2;
+    FL_DISPATCH(w_dtype, TW, rc = fl_launch(rglru_gates_kernel<TW>, dim3(tiles, blocks, z), dim3(256), smem, stream,
+                                            (const float*)u, s_ld, (const TW*)w_a, (const TW*)w_i, b_a, b_i, rate, a, bx,
+                                            s_ld, n_tokens, width, bw));
+    if (rc) return rc;
+    FL_DISPATCH(dtype, T, return fl_launch(rglru_scan_kernel<T>, dim3(n_requests, (width + 127) / 128), dim3(128), 0, stream,
+                                           (const float*)a, (const float*)bx, s_ld, (const T*)proj, ld, bias, state,
+                                           state_stride, req_start, req_ctx, req_qlen, req_slot, (T*)out, out_ld, width,
+                                           taps));
+    return 0;
+}

@@ -12,6 +12,8 @@
 // A cache page is [kv_heads, page_size, dim + vdim]: a token's key, then its value (the blended one).
 //
 //   sink_prep             per token: biases, both norms, the blend; q to its buffer, k and v to the token's cache rows
+//   head_prep             the per-head form of the preparation, for attention whose q and k are normed head by head and
+//                         rotated (see there); head_gate multiplies a head's result by a sigmoid
 //   sink_attention_simt   per (token, query head): CUDA cores, any sizes, bfloat16 or true 32-bit; key tiles start at
 //                         multiples of 128 of the absolute position and tiles without a visible key are skipped, so
 //                         every sum's order depends on the token's own position only
@@ -87,6 +89,127 @@ FL_API int fl_sink_prep(const void* proj, int dtype, long ld, const float* bias,
     return 0;
 }
 
+// ------------------------------------------------------------------ preparation head by head
+// proj row: heads x dim queries, kv_heads x dim keys and (unless the keys serve as values) kv_heads x vdim values; bias:
+// the same layout, float, or null.  Each query and key head passes, in this order:
+//   norm_mode 1: an RMS norm over its dim elements, times q_w / k_w ([dim], shared by the heads; null: no weight)
+//   rot > 0:     the rotation of its first `rot` dimensions by the row `position` of cos / sin ([positions, rot / 2]);
+//                pair i is (2i, 2i + 1) with `interleaved`, else (i, i + rot / 2)
+//   norm_mode 2: an RMS norm without weight, after the rotation
+//   queries:     times 1 + temp_coef * ln(floor((position + 1) / temp_every) + 1)      (temp_every <= 0: not)
+// q goes to q_out, k to the token's cache row.  The value beside it is the projected value with its bias, or, with
+// v_from_k, the key as projected (with its bias, before norm and rotation); vdim = dim then.
+template <typename T, typename TQ>
+__global__ void __launch_bounds__(256) head_prep_kernel(
+    const T* __restrict__ proj, long ld, const float* __restrict__ bias, const float* __restrict__ q_w,
+    const float* __restrict__ k_w, int norm_mode, float eps, int rot, int interleaved, const float* __restrict__ cos_t,
+    const float* __restrict__ sin_t, const int* __restrict__ positions, float temp_coef, int temp_every, int v_from_k,
+    TQ* __restrict__ q_out, long q_ld, int heads, int kv_heads, int dim, int vdim, const int* __restrict__ slots,
+    T* __restrict__ cache, long page_stride, int page_size) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float prep_s[];                                 // [8 warps][dim]
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T* row = proj + (long)t * ld;
+    const int nq = heads * dim, nk = kv_heads * dim;
+    const int pos = positions[t];
+    const int half = rot / 2;
+    const int slot = slots[t];
+    const long page = slot / page_size;
+    const int off = slot - (int)page * page_size;
+    const int row_w = dim + vdim;
+    T* dst = cache + page * page_stride + (long)off * row_w;          // head g's row: + g * page_size * row_w
+    const long head_stride = (long)page_size * row_w;
+    float* buf = prep_s + warp * dim;
+    float factor = 1.0f;
+    if (temp_every > 0) factor = 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f);
+    for (int idx = warp; idx < heads + kv_heads; idx += 8) {
+        const bool is_q = idx < heads;
+        const int col0 = is_q ? idx * dim : nq + (idx - heads) * dim;
+        T* krow = dst + (long)(idx - heads) * head_stride;
+        float ss = 0.0f;
+        for (int d = lane; d < dim; d += 32) {
+            const float a = to_f32<T>(row[col0 + d]) + (bias ? bias[col0 + d] : 0.0f);
+            buf[d] = a;
+            ss += a * a;
+            if (!is_q && v_from_k) krow[dim + d] = from_f32<T>(a);
+        }
+        __syncwarp();
+        if (norm_mode == 1) {
+            const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dim + eps);
+            const float* w = is_q ? q_w : k_w;
+            for (int d = lane; d < dim; d += 32) buf[d] = buf[d] * inv * (w ? w[d] : 1.0f);
+            __syncwarp();
+        }
+        for (int i = lane; i < half; i += 32) {
+            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+            const float c = cos_t[(long)pos * half + i], sn = sin_t[(long)pos * half + i];
+            const float a = buf[ia], b = buf[ib];
+            buf[ia] = a * c - b * sn;
+            buf[ib] = b * c + a * sn;
+        }
+        __syncwarp();
+        float inv = 1.0f;
+        if (norm_mode == 2) {
+            float s2 = 0.0f;
+            for (int d = lane; d < dim; d += 32) s2 += buf[d] * buf[d];
+            inv = 1.0f / sqrtf(warp_sum(s2) / (float)dim + eps);
+        }
+        if (is_q) {
+            TQ* qo = q_out + (long)t * q_ld + (long)idx * dim;
+            for (int d = lane; d < dim; d += 32) qo[d] = from_f32<TQ>(buf[d] * inv * factor);
+        } else {
+            for (int d = lane; d < dim; d += 32) krow[d] = from_f32<T>(buf[d] * inv);
+        }
+        __syncwarp();                                                 // buf is rewritten for the next head
+    }
+    if (!v_from_k) {
+        const int nv = kv_heads * vdim;
+        for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+            const int g = i / vdim, d = i - g * vdim;
+            dst[g * head_stride + dim + d] = from_f32<T>(to_f32<T>(row[nq + nk + i]) + (bias ? bias[nq + nk + i] : 0.0f));
+        }
+    }
+}
+
+FL_API int fl_head_prep(const void* proj, int dtype, long ld, const float* bias, const float* q_w, const float* k_w,
+                        int norm_mode, float eps, int rot, int interleaved, const float* cos_t, const float* sin_t,
+                        const int* positions, float temp_coef, int temp_every, int v_from_k, void* q_out, int q_dtype,
+                        long q_ld, int n_tokens, int heads, int kv_heads, int dim, int vdim, const int* slots, void* cache,
+                        long page_stride, int page_size, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (norm_mode < 0 || norm_mode > 2 || rot < 0 || rot > dim || (rot & 1) || (rot > 0 && (cos_t == nullptr || sin_t == nullptr)) ||
+        (v_from_k && vdim != dim) || (size_t)dim * 8 * sizeof(float) > 48 * 1024 || cache == nullptr)
+        return (int)cudaErrorInvalidValue;
+    FL_DISPATCH(dtype, T, FL_DISPATCH(q_dtype, TQ,
+        return fl_launch(head_prep_kernel<T, TQ>, dim3(n_tokens), dim3(256), (size_t)dim * 8 * sizeof(float), stream,
+                         (const T*)proj, ld, bias, q_w, k_w, norm_mode, eps, rot, interleaved, cos_t, sin_t, positions,
+                         temp_coef, temp_every, v_from_k, (TQ*)q_out, q_ld, heads, kv_heads, dim, vdim, slots, (T*)cache,
+                         page_stride, page_size)));
+    return 0;
+}
+
+// x[t, h * vdim + d] *= sigmoid(gate[t, h]): one number per token and head on the head's whole result.
+template <typename T>
+__global__ void __launch_bounds__(256) head_gate_kernel(T* __restrict__ x, long x_ld, const T* __restrict__ gate, long g_ld,
+                                                        int heads, int vdim) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < heads * vdim; i += blockDim.x) {
+        const float g = to_f32<T>(gate[(long)t * g_ld + i / vdim]);
+        x[(long)t * x_ld + i] = from_f32<T>(to_f32<T>(x[(long)t * x_ld + i]) / (1.0f + expf(-g)));
+    }
+}
+
+FL_API int fl_head_gate(void* x, int dtype, long x_ld, const void* gate, long g_ld, int n_tokens, int heads, int vdim,
+                        cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    FL_DISPATCH(dtype, T, return fl_launch(head_gate_kernel<T>, dim3(n_tokens), dim3(256), 0, stream, (T*)x, x_ld,
+                                           (const T*)gate, g_ld, heads, vdim));
+    return 0;
+}
+
 // The score of key j for a query at `pos` from the dot product.
 __device__ __forceinline__ float sink_score(float dot, float scale, float cap, const int* bucket_of, int n_dist,
                                             const float* rel, int heads, int h, int dist) {
@@ -100,8 +223,8 @@ template <typename T, typename TQ>
 __global__ void __launch_bounds__(SINK_TILE) sink_attention_simt_kernel(
     const TQ* __restrict__ q, long q_ld, T* __restrict__ out, long out_ld, const T* __restrict__ cache, long page_stride,
     int page_size, const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req,
-    const int* __restrict__ positions, int heads, int kv_heads, int dim, int vdim, int window, int keep_first, float scale,
-    float cap, const int* __restrict__ bucket_of, int n_dist, const float* __restrict__ rel,
+    const int* __restrict__ positions, int heads, int kv_heads, int dim, int vdim, int window, int keep_first, int chunk,
+    float scale, float cap, const int* __restrict__ bucket_of, int n_dist, const float* __restrict__ rel,
     const float* __restrict__ sink) {
     pdl_wait();
     pdl_trigger();
@@ -115,8 +238,9 @@ __global__ void __launch_bounds__(SINK_TILE) sink_attention_simt_kernel(
     const int g = h / (heads / kv_heads);
     const int pos = positions[t];
     const int* bt = block_table + (long)tok_req[t] * bt_stride;
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int kept = min(keep_first, lo);                             // keys [0, kept) are seen beside [lo, pos]
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);                 // a query sees its own chunk of positions only
+    const int kept = window > 0 ? min(keep_first, lo) : 0;            // keys [0, kept) are seen beside [lo, pos]
     const int row_w = dim + vdim;
 
     const TQ* qr = q + (long)t * q_ld + (long)h * dim;
@@ -171,12 +295,14 @@ __global__ void __launch_bounds__(SINK_TILE) sink_attention_simt_kernel(
 }
 
 // q: [n_tokens, q_ld], head h at columns [h * dim, (h + 1) * dim); out: [n_tokens, out_ld], head h at columns
-// [h * vdim, (h + 1) * vdim).  window <= 0: all keys.  bucket_of: [n_dist] rows of rel ([rows, heads] float) by distance.
+// [h * vdim, (h + 1) * vdim).  window <= 0: all keys.  chunk > 0: only keys at or after the last multiple of `chunk`
+// at or below the query's position.  bucket_of: [n_dist] rows of rel ([rows, heads] float) by distance.
 FL_API int fl_sink_attention_simt(const void* q, int q_dtype, long q_ld, void* out, long out_ld, const void* cache, int dtype,
                                   long page_stride, int page_size, const int* block_table, int bt_stride,
                                   const int* tok_req, const int* positions, int n_tokens, int heads, int kv_heads, int dim,
-                                  int vdim, int window, int keep_first, float scale, float cap, const int* bucket_of,
-                                  int n_dist, const float* rel, const float* sink, cudaStream_t stream) {
+                                  int vdim, int window, int keep_first, int chunk, float scale, float cap,
+                                  const int* bucket_of, int n_dist, const float* rel, const float* sink,
+                                  cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (vdim < 1 || vdim > 2 * SINK_TILE || dim < 1 || dim > 4096 || heads > 65535 || heads % kv_heads ||
         (rel != nullptr && (bucket_of == nullptr || n_dist < 1)))
@@ -186,7 +312,7 @@ FL_API int fl_sink_attention_simt(const void* q, int q_dtype, long q_ld, void* o
     FL_DISPATCH(dtype, T, FL_DISPATCH(q_dtype, TQ,
         return fl_launch(sink_attention_simt_kernel<T, TQ>, grid, dim3(SINK_TILE), smem, stream, (const TQ*)q, q_ld, (T*)out,
                          out_ld, (const T*)cache, page_stride, page_size, block_table, bt_stride, tok_req, positions, heads,
-                         kv_heads, dim, vdim, window, keep_first, scale, cap, bucket_of, n_dist, rel, sink)));
+                         kv_heads, dim, vdim, window, keep_first, chunk, scale, cap, bucket_of, n_dist, rel, sink)));
     return 0;
 }
 
@@ -220,8 +346,8 @@ __global__ void __launch_bounds__(SINK_SPLIT) sink_decode_kernel(
     const T* __restrict__ q, long q_ld, const T* __restrict__ cache, long page_stride, int page_size,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_req, const int* __restrict__ positions,
     const int* __restrict__ decode_tokens, float* __restrict__ partial, int n_splits, int kept_splits, int heads,
-    int kv_heads, int dim, int vdim, int window, int keep_first, float scale, float cap, const int* __restrict__ bucket_of,
-    int n_dist, const float* __restrict__ rel, int vec8) {
+    int kv_heads, int dim, int vdim, int window, int keep_first, int chunk, float scale, float cap,
+    const int* __restrict__ bucket_of, int n_dist, const float* __restrict__ rel, int vec8) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ __align__(16) unsigned char dec_smem[];
@@ -232,7 +358,8 @@ __global__ void __launch_bounds__(SINK_SPLIT) sink_decode_kernel(
     const int t = decode_tokens[blockIdx.x], g = blockIdx.y, split = blockIdx.z, tid = threadIdx.x;
     const int group = heads / kv_heads;
     const int pos = positions[t];
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
     const int kept = window > 0 ? min(keep_first, lo) : 0;
     // the split's keys: [first, first + 128) cut to [from, to)
     int first, from, to;
@@ -397,7 +524,7 @@ FL_API int fl_sink_decode_takes(int heads, int kv_heads, int dim, int vdim) {
 FL_API int fl_sink_decode(const void* q, int dtype, long q_ld, void* out, long out_ld, const void* cache, long page_stride,
                           int page_size, const int* block_table, int bt_stride, const int* tok_req, const int* positions,
                           const int* decode_tokens, int n_decode, float* partial, int n_splits, int kept_splits, int heads,
-                          int kv_heads, int dim, int vdim, int window, int keep_first, float scale, float cap,
+                          int kv_heads, int dim, int vdim, int window, int keep_first, int chunk, float scale, float cap,
                           const int* bucket_of, int n_dist, const float* rel, const float* sink, cudaStream_t stream) {
     if (n_decode <= 0) return 0;
     if (!fl_sink_decode_takes(heads, kv_heads, dim, vdim) || n_splits < 1 || n_splits > 65535 || kv_heads > 65535 ||
@@ -414,7 +541,7 @@ FL_API int fl_sink_decode(const void* q, int dtype, long q_ld, void* out, long o
     FL_DISPATCH(dtype, T, rc = fl_launch(sink_decode_kernel<T, G>, grid, dim3(SINK_SPLIT), smem, stream, (const T*)q, \
                                          q_ld, (const T*)cache, page_stride, page_size, block_table, bt_stride,      \
                                          tok_req, positions, decode_tokens, partial, n_splits, kept_splits, heads,   \
-                                         kv_heads, dim, vdim, window, keep_first, scale, cap, bucket_of, n_dist, rel, vec8))
+                                         kv_heads, dim, vdim, window, keep_first, chunk, scale, cap, bucket_of, n_dist, rel, vec8))
     if (gp == 1) { FL_SINK_DECODE(1); }
     else if (gp == 2) { FL_SINK_DECODE(2); }
     else if (gp == 4) { FL_SINK_DECODE(4); }

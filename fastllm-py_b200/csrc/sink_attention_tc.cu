@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(STC_THREADS, 3) sink_attention_tc_kernel(
     const bf16* __restrict__ q, long q_ld, bf16* __restrict__ out, long out_ld, const bf16* __restrict__ cache,
     long page_stride, int page_size, int page_shift, const int* __restrict__ block_table, int bt_stride,
     const int* __restrict__ req_start, const int* __restrict__ req_ctx, const int* __restrict__ req_qlen,
-    int n_requests, int include_single, int heads, int kv_heads, int window, int keep_first, float scale, float cap,
+    int n_requests, int include_single, int heads, int kv_heads, int window, int keep_first, int chunk, float scale, float cap,
     const int* __restrict__ row_of, int n_dist, const float* __restrict__ rel, const float* __restrict__ sink) {
     pdl_wait();
     pdl_trigger();
@@ -102,7 +102,8 @@ __global__ void __launch_bounds__(STC_THREADS, 3) sink_attention_tc_kernel(
     const int tok0 = req_start[req] + row0;
     const int rows_here = min(STC_BM, q_len - row0);
     const int pos_first = ctx + row0, pos_last = ctx + row0 + rows_here - 1;
-    const int lo_tile = window > 0 ? max(0, pos_first - window + 1) : 0;
+    int lo_tile = window > 0 ? max(0, pos_first - window + 1) : 0;
+    if (chunk > 0) lo_tile = max(lo_tile, pos_first / chunk * chunk);        // a row sees its own chunk of positions only
     const int keep = window > 0 ? keep_first : 0;
     const int kb_begin = lo_tile / STC_BN, kb_end = pos_last / STC_BN + 1;
     const int n_kept = min((min(keep, pos_last + 1) + STC_BN - 1) / STC_BN, kb_begin);   // blocks of kept tokens before the window's
@@ -152,6 +153,7 @@ __global__ void __launch_bounds__(STC_THREADS, 3) sink_attention_tc_kernel(
     m_run[0] = m_run[1] = sink != nullptr ? sink[h] * STC_LOG2E : -CUDART_INF_F;
     l_run[0] = l_run[1] = (sink != nullptr && tq == 0) ? 1.0f : 0.0f;
     const int pos_row[2] = {ctx + row0 + warp * 16 + g, ctx + row0 + warp * 16 + g + 8};
+    const int chunk_row[2] = {chunk > 0 ? pos_row[0] / chunk * chunk : 0, chunk > 0 ? pos_row[1] / chunk * chunk : 0};
     const float inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
 
     load_q();
@@ -172,8 +174,10 @@ __global__ void __launch_bounds__(STC_THREADS, 3) sink_attention_tc_kernel(
         const bf16* rt = Rs + stage * STC_BN * STC_KP;
         const int warp_pos_lo = ctx + row0 + warp * 16, warp_pos_hi = warp_pos_lo + 15;
         const int b_lo = kb * STC_BN, b_hi = b_lo + STC_BN - 1;
-        const bool all_seen = b_hi <= warp_pos_lo && (window <= 0 || b_lo > warp_pos_hi - window || b_hi < keep);
-        const bool none_seen = b_lo > warp_pos_hi || (window > 0 && b_hi <= warp_pos_lo - window && b_lo >= keep);
+        const bool all_seen = b_hi <= warp_pos_lo && (window <= 0 || b_lo > warp_pos_hi - window || b_hi < keep) &&
+                              (chunk <= 0 || b_lo >= warp_pos_hi / chunk * chunk);
+        const bool none_seen = b_lo > warp_pos_hi || (window > 0 && b_hi <= warp_pos_lo - window && b_lo >= keep) ||
+                               (chunk > 0 && b_hi < warp_pos_lo / chunk * chunk);
         if (has_rows && !none_seen) {
             // ---- S = Q K^T for this warp's 16 rows and the block's 64 keys
             float s[STC_BN / 8][4];
@@ -202,7 +206,7 @@ __global__ void __launch_bounds__(STC_THREADS, 3) sink_attention_tc_kernel(
                 for (int e = 0; e < 4; ++e) {
                     const int j = b_lo + nt * 8 + 2 * tq + (e & 1);
                     const int pr = pos_row[e >> 1];
-                    const bool seen = all_seen || (j <= pr && (window <= 0 || j > pr - window || j < keep));
+                    const bool seen = all_seen || (j <= pr && (window <= 0 || j > pr - window || j < keep) && j >= chunk_row[e >> 1]);
                     float v = -CUDART_INF_F;
                     if (seen) {
                         v = s[nt][e] * scale;
@@ -285,12 +289,13 @@ FL_API int fl_sink_attention_tc_vdim() { return SINK_VDIM; }
 
 // Every request r of the step with req_qlen[r] > 1 (or >= 1 with include_single) gets attention for its rows req_start[r] .. req_start[r] + req_qlen[r] - 1 at positions
 // req_ctx[r] + i over its cached rows.  n_tokens bounds the number of 64-row tiles.  cap <= 0: no cap; rel null: no
-// bias; sink null: no sink; window <= 0: every earlier key.
+// bias; sink null: no sink; window <= 0: every earlier key; chunk > 0: only keys at or after the last multiple of
+// `chunk` at or below the query's position.
 FL_API int fl_sink_attention_tc(const void* q, long q_ld, void* out, long out_ld, const void* cache, long page_stride,
                                 int page_size, const int* block_table, int bt_stride, const int* req_start,
                                 const int* req_ctx, const int* req_qlen, int n_requests, int n_tokens,
                                 int include_single, int heads,
-                                int kv_heads, int window, int keep_first, float scale, float cap, const int* row_of,
+                                int kv_heads, int window, int keep_first, int chunk, float scale, float cap, const int* row_of,
                                 int n_dist, const float* rel, const float* sink, cudaStream_t stream) {
     if (n_requests <= 0 || n_tokens <= 0) return 0;
     if (heads > 65535 || heads % kv_heads || (rel != nullptr && (row_of == nullptr || n_dist < 1)))
@@ -313,6 +318,6 @@ FL_API int fl_sink_attention_tc(const void* q, long q_ld, void* out, long out_ld
     dim3 grid(max_tiles, heads);
     return fl_launch(sink_attention_tc_kernel, grid, dim3(STC_THREADS), smem, stream, (const bf16*)q, q_ld, (bf16*)out,
                      out_ld, (const bf16*)cache, page_stride, page_size, page_shift, block_table, bt_stride, req_start,
-                     req_ctx, req_qlen, n_requests, include_single, heads, kv_heads, window, keep_first, scale, cap, row_of, n_dist, rel,
+                     req_ctx, req_qlen, n_requests, include_single, heads, kv_heads, window, keep_first, chunk, scale, cap, row_of, n_dist, rel,
                      sink);
 }

@@ -3,7 +3,7 @@ from .ops import BASE_LIBRARIES, BF16_LIBRARIES
 
 # what parts name (`native_libraries`): every one of them, for a build of everything
 PART_LIBRARIES = ["rope_kv", "attention_simt", "delta_rule", "latent_attention", "gemm_mma", "moe", "diff_attention",
-                  "retention", "gated_block", "sink_attention"]
+                  "retention", "gated_block", "sink_attention", "norm_mix", "rglru", "gla"]
 
 DEFAULT_HEAD_DIMS = (128,)
 

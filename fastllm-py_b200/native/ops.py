@@ -232,10 +232,10 @@ def glu(gate_up, out, activation: str = "silu", params=(0.0, 0.0)):
               out.shape[1], activation_code(activation), float(params[0]), float(params[1]), _stream()), "glu")
 
 
-# Gated units f(g, u) of a gate value and an up value.  silu, relu, gelu_tanh: act(g) * u.
+# Gated units f(g, u) of a gate value and an up value.  silu, relu, gelu_tanh, relu_squared: act(g) * u.
 # clamped_swish with params (limit, slope): g' = min(g, limit), u' = clamp(u, -limit, limit),
 # f = g' * sigmoid(slope * g') * (u' + 1).
-ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "clamped_swish": 3}
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "clamped_swish": 3, "relu_squared": 4}
 
 
 def activation_code(name: str) -> int:
@@ -691,20 +691,21 @@ def sink_prep(proj, bias, q_w, k_w, eps, q_out, heads, kv_heads, dim, vdim, v_mo
 
 
 def sink_attention_simt(q, out, cache, block_table, tok_req, positions, heads, kv_heads, dim, vdim, window, keep_first,
-                        scale, cap, bucket_of, rel, sink, page_size):
+                        scale, cap, bucket_of, rel, sink, page_size, chunk=None):
     """Attention of every token over its request's visible keys (the last `window` and the first `keep_first`), scores
     capped (`cap` None or 0: not), biased by `rel[bucket_of[distance]]` and with `sink` in the denominator (each may be
-    None).  CUDA cores, any sizes, both number formats."""
+    None).  With `chunk` a query sees only keys at or after the last multiple of `chunk` at or below its own position.
+    CUDA cores, any sizes, both number formats."""
     _require_cuda(q, out, cache, block_table, tok_req, positions, bucket_of, rel, sink)
     if vdim > 256:
         raise KernelError(f"sink_attention: value size {vdim} is beyond the kernel's limit of 256")
     fn = _fn("sink_attention", "fl_sink_attention_simt",
              [c_void_p, c_int, c_long, c_void_p, c_long, c_void_p, c_int, c_long, c_int, c_void_p, c_int, c_void_p, c_void_p,
-              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p, c_void_p,
+              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p, c_void_p,
               c_void_p])
     _check(fn(_ptr(q), dtype_code(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), dtype_code(cache), cache.stride(0), page_size,
               _ptr(block_table), block_table.stride(0), _ptr(tok_req), _ptr(positions), q.shape[0], heads, kv_heads, dim,
-              vdim, int(window or 0), int(keep_first or 0), float(scale), float(cap or 0.0), _ptr(bucket_of),
+              vdim, int(window or 0), int(keep_first or 0), int(chunk or 0), float(scale), float(cap or 0.0), _ptr(bucket_of),
               0 if bucket_of is None else bucket_of.numel(), _ptr(rel), _ptr(sink), _stream()), "sink_attention_simt")
 
 
@@ -718,7 +719,7 @@ def sink_tc_library(dim: int, vdim: int):
 
 
 def sink_attention_tc(q, out, cache, block_table, step, heads, kv_heads, dim, vdim, window, keep_first, scale, cap,
-                      bucket_of, rel, sink, page_size, include_single=True):
+                      bucket_of, rel, sink, page_size, include_single=True, chunk=None):
     """`sink_attention_simt` on tensor cores: q, cache and out bfloat16; one build per (dim, vdim); 64 rows of a
     request and one head per block, single tokens as tiles of one row (left out with include_single=False)."""
     _require_cuda(q, out, cache, block_table, bucket_of, rel, sink)
@@ -727,11 +728,11 @@ def sink_attention_tc(q, out, cache, block_table, step, heads, kv_heads, dim, vd
     name, defines = sink_tc_library(dim, vdim)
     fn = _fn(name, "fl_sink_attention_tc", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_int,
                                             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                            c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p], defines)
+                                            c_int, c_float, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p], defines)
     _check(fn(_ptr(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), cache.stride(0), page_size, _ptr(block_table),
               block_table.stride(0), _ptr(step.req_start), _ptr(step.req_ctx), _ptr(step.req_qlen), step.n_requests,
-              q.shape[0], int(include_single), heads, kv_heads, int(window or 0), int(keep_first or 0), float(scale),
-              float(cap or 0.0), _ptr(bucket_of), 0 if bucket_of is None else bucket_of.numel(), _ptr(rel), _ptr(sink),
+              q.shape[0], int(include_single), heads, kv_heads, int(window or 0), int(keep_first or 0), int(chunk or 0),
+              float(scale), float(cap or 0.0), _ptr(bucket_of), 0 if bucket_of is None else bucket_of.numel(), _ptr(rel), _ptr(sink),
               _stream()), "sink_attention_tc")
 
 
@@ -744,15 +745,17 @@ def sink_decode_takes(heads: int, kv_heads: int, dim: int, vdim: int) -> bool:
     return bool(fn(heads, kv_heads, dim, vdim))
 
 
-def sink_decode_splits(window, keep_first: int, longest: int):
+def sink_decode_splits(window, keep_first: int, longest: int, chunk=None):
     """(splits in all, splits that walk the kept first tokens) for single tokens of sequences up to `longest`."""
     kept = -(-int(keep_first or 0) // SINK_SPLIT) if window else 0
     span = min(int(window), longest) if window else longest
+    if chunk:
+        span = min(span, int(chunk))
     return kept + (max(span, 1) - 1) // SINK_SPLIT + 2, kept
 
 
 def sink_decode(q, out, cache, block_table, tok_req, positions, decode_tokens, partial, n_splits, kept_splits, heads,
-                kv_heads, dim, vdim, window, keep_first, scale, cap, bucket_of, rel, sink, page_size):
+                kv_heads, dim, vdim, window, keep_first, scale, cap, bucket_of, rel, sink, page_size, chunk=None):
     """Sink attention for the rows `decode_tokens` of q (each the single token of its request): the keys split over
     blocks of 128, every query head of a key/value head served by the block that reads its rows, then a merge with
     the sink.  partial: float32, decode tokens * heads * n_splits * (vdim + 2)."""
@@ -764,44 +767,202 @@ def sink_decode(q, out, cache, block_table, tok_req, positions, decode_tokens, p
         raise KernelError("sink_decode: q, cache and out share a dtype")
     fn = _fn("sink_attention", "fl_sink_decode",
              [c_void_p, c_int, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_int, c_void_p, c_void_p,
-              c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p,
-              c_int, c_void_p, c_void_p, c_void_p])
+              c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+              c_void_p, c_int, c_void_p, c_void_p, c_void_p])
     _check(fn(_ptr(q), dtype_code(q), _ld(q), _ptr(out), _ld(out), _ptr(cache), cache.stride(0), page_size,
               _ptr(block_table), block_table.stride(0), _ptr(tok_req), _ptr(positions), _ptr(decode_tokens), n,
               _ptr(partial), int(n_splits), int(kept_splits), heads, kv_heads, dim, vdim, int(window or 0),
-              int(keep_first or 0), float(scale), float(cap or 0.0), _ptr(bucket_of),
+              int(keep_first or 0), int(chunk or 0), float(scale), float(cap or 0.0), _ptr(bucket_of),
               0 if bucket_of is None else bucket_of.numel(), _ptr(rel), _ptr(sink), _stream()), "sink_decode", 2)
+
+
+def head_prep(proj, bias, q_w, k_w, norm_mode, eps, rot, interleaved, cos, sin, positions, temp, v_from_k, q_out, heads,
+              kv_heads, dim, vdim, slots, cache, page_size):
+    """The preparation of attention head by head: biases; norm_mode 1: an RMS norm of every query and key head times
+    q_w / k_w ([dim] float, or None) before the rotation, 2: one without weight after it, 0: none; the rotation of a
+    head's first `rot` dimensions, pairs (2i, 2i + 1) with `interleaved`, else (i, i + rot / 2); queries times
+    1 + coef * ln(floor((position + 1) / every) + 1) with temp = (coef, every); q to `q_out`, k and v into the tokens'
+    rows of `cache` ([pages, kv_heads, page_size, dim + vdim]); with `v_from_k` the value is the key as projected."""
+    _require_cuda(proj, bias, q_w, k_w, cos, sin, positions, q_out, slots, cache)
+    if cache.dtype != proj.dtype or not cache.is_contiguous():
+        raise KernelError("head_prep: the cache must be contiguous and of the activations' dtype")
+    for v in (bias, q_w, k_w, cos, sin):
+        if v is not None and v.dtype != torch.float32:
+            raise KernelError("head_prep: biases, norm weights and the rotation's tables are float32")
+    if rot and cos.shape[1] != rot // 2:
+        raise KernelError("head_prep: the rotation's tables do not fit the rotated dimensions")
+    coef, every = temp if temp is not None else (0.0, 0)
+    fn = _fn("sink_attention", "fl_head_prep",
+             [c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
+              c_float, c_int, c_int, c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_long,
+              c_int, c_void_p])
+    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(bias), _ptr(q_w), _ptr(k_w), int(norm_mode), float(eps),
+              int(rot or 0), int(bool(interleaved)), _ptr(cos) if rot else None, _ptr(sin) if rot else None,
+              _ptr(positions), float(coef), int(every), int(bool(v_from_k)), _ptr(q_out), dtype_code(q_out), _ld(q_out),
+              proj.shape[0], heads, kv_heads, dim, vdim, _ptr(slots), _ptr(cache), cache.stride(0), page_size, _stream()),
+           "head_prep")
+
+
+def head_gate(x, gate, heads, vdim):
+    """x[t, h * vdim + d] *= sigmoid(gate[t, h])."""
+    _require_cuda(x, gate)
+    if x.dtype != gate.dtype:
+        raise KernelError("head_gate: x and the gate share a dtype")
+    fn = _fn("sink_attention", "fl_head_gate", [c_void_p, c_int, c_long, c_void_p, c_long, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(x), dtype_code(x), _ld(x), _ptr(gate), _ld(gate), x.shape[0], heads, vdim, _stream()), "head_gate")
+
+
+# ----------------------------------------------- layer norm, mixes, activation
+
+def add_layernorm(resid, delta, scale, weight, bias, out, eps, rows=None):
+    """resid += scale * delta (float32, written back unless rows are gathered; delta None: nothing to add);
+    out = (resid - mean) / sqrt(var + eps) * weight + bias."""
+    _require_cuda(resid, delta, weight, bias, out, rows)
+    if resid.dtype != torch.float32 or (bias is not None and bias.dtype != weight.dtype):
+        raise KernelError("add_layernorm: the residual stream is float32; weight and bias share a dtype")
+    fn = _fn("norm_mix", "fl_add_layernorm", [c_void_p, c_long, c_void_p, c_int, c_long, c_float, c_void_p, c_void_p, c_int,
+                                              c_void_p, c_int, c_long, c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(fn(_ptr(resid), _ld(resid), _ptr(delta), F32 if delta is None else dtype_code(delta),
+              0 if delta is None else _ld(delta), float(scale), _ptr(weight), _ptr(bias), dtype_code(weight), _ptr(out),
+              dtype_code(out), _ld(out), out.shape[0], resid.shape[1], float(eps), _ptr(rows), _stream()), "add_layernorm")
+
+
+def rms_mix(a, b, w_a, w_b, out, eps, weight=0.5):
+    """out = weight * (a / rms(a) * w_a + b / rms(b) * w_b), row by row."""
+    _require_cuda(a, b, w_a, w_b, out)
+    if a.dtype != b.dtype or a.dtype != out.dtype or w_a.dtype != w_b.dtype:
+        raise KernelError("rms_mix: a, b and out share a dtype, and so do the weights")
+    fn = _fn("norm_mix", "fl_rms_mix", [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                                        c_long, c_int, c_int, c_float, c_float, c_void_p])
+    _check(fn(_ptr(a), _ld(a), _ptr(b), _ld(b), dtype_code(a), _ptr(w_a), _ptr(w_b), dtype_code(w_a), _ptr(out), _ld(out),
+              a.shape[0], a.shape[1], float(eps), float(weight), _stream()), "rms_mix")
+
+
+def scaled_add(resid, delta, scale):
+    """resid += scale * delta."""
+    _require_cuda(resid, delta)
+    if resid.dtype != torch.float32:
+        raise KernelError("scaled_add: the residual stream must be float32")
+    fn = _fn("norm_mix", "fl_scaled_add", [c_void_p, c_long, c_void_p, c_int, c_long, c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(resid), _ld(resid), _ptr(delta), dtype_code(delta), _ld(delta), resid.shape[0], resid.shape[1],
+              float(scale), _stream()), "scaled_add")
+
+
+def activation(x, out, name: str, params=(0.0, 0.0)):
+    """out = f(x, 1) for the gated units' f (ACTIVATIONS): an activation of one argument."""
+    _require_cuda(x, out)
+    if x.dtype != out.dtype:
+        raise KernelError("activation: input and output must have one dtype")
+    fn = _fn("norm_mix", "fl_activation", [c_void_p, c_int, c_long, c_void_p, c_long, c_int, c_int, c_int, c_float, c_float,
+                                           c_void_p])
+    _check(fn(_ptr(x), dtype_code(x), _ld(x), _ptr(out), _ld(out), x.shape[0], x.shape[1], activation_code(name),
+              float(params[0]), float(params[1]), _stream()), "activation")
+
+
+# ---------------------------------------------- gated recurrence per channel
+
+def rglru(proj, bias, conv_w, conv_b, w_a, w_i, b_a, b_i, rate, state, step, u, a, bx, out, width, blocks, taps):
+    """The gated linear recurrence per channel over the step's tokens.  proj [N, 2 width] = gate branch | input branch
+    before their biases (`bias`, float32 [2 width]); the input branch passes a causal convolution (`conv_w`
+    [width, taps], `conv_b`), the gates r and i are sigmoids of block-diagonal products of it (`w_a`, `w_i`
+    [blocks, width / blocks, width / blocks], `b_a`, `b_i` [width]), a = exp(rate * r), S <- a S + sqrt(1 - a^2) i u;
+    out = S * gelu_tanh(gate branch).  state rows: [S | the last taps - 1 inputs] float32; u, a, bx: float32 [N, width]."""
+    _require_cuda(proj, bias, conv_w, conv_b, w_a, w_i, b_a, b_i, rate, state, u, a, bx, out)
+    for v in (bias, conv_w, conv_b, b_a, b_i, rate, state, u, a, bx):
+        if v.dtype != torch.float32:
+            raise KernelError("rglru: biases, convolution, rates, state and scratch are float32")
+    if w_a.dtype != w_i.dtype or not w_a.is_contiguous() or not w_i.is_contiguous() or out.dtype != proj.dtype:
+        raise KernelError("rglru: the gate matrices share a dtype and are contiguous; out has the activations' dtype")
+    if state.stride(0) < width * taps or _ld(u) != _ld(a) or _ld(u) != _ld(bx):
+        raise KernelError("rglru: state rows hold width * taps floats; u, a and bx share a row pitch")
+    fn = _fn("rglru", "fl_rglru", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                   c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_long, c_int,
+                                   c_int, c_int, c_void_p])
+    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(bias), _ptr(conv_w), _ptr(conv_b), _ptr(w_a), _ptr(w_i),
+              dtype_code(w_a), _ptr(b_a), _ptr(b_i), _ptr(rate), _ptr(state), state.stride(0), _ptr(step.tok_req),
+              _ptr(step.positions), _ptr(step.req_start), _ptr(step.req_ctx), _ptr(step.req_qlen), _ptr(step.req_slot),
+              proj.shape[0], step.n_requests, _ptr(u), _ptr(a), _ptr(bx), _ld(u), _ptr(out), _ld(out), width, blocks, taps,
+              _stream()), "rglru", 3)
+
+
+# ---------------------------------------------------- gated linear attention
+
+def gla_prep(proj, w2, b2, work, heads, dim, vdim, rank, q_scale, tau):
+    """proj columns q | k (heads x dim each) | v | gate (heads x vdim each) | low (rank): q times `q_scale`, k, the decay
+    alpha = sigmoid(W_2 low + b_2)^(1 / tau) per key channel and v into the float32 columns q | k | alpha | v of `work`."""
+    _require_cuda(proj, w2, b2, work)
+    if work.dtype != torch.float32 or w2.dtype != torch.float32 or b2.dtype != torch.float32 or not w2.is_contiguous():
+        raise KernelError("gla_prep: the work buffer, W_2 and b_2 are float32")
+    fn = _fn("gla", "fl_gla_prep", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int,
+                                    c_int, c_float, c_float, c_void_p])
+    _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(w2), _ptr(b2), _ptr(work), _ld(work), proj.shape[0], heads, dim,
+              vdim, rank, float(q_scale), float(tau), _stream()), "gla_prep")
+
+
+def gla_scan(work, o, state, step, heads, dim, vdim):
+    """Per request and head S <- diag(alpha) S + k v^T, o = S^T q over the step's tokens; q | k | alpha | v are the
+    float32 columns of `work`, `o` float32 [N, heads * vdim]; state rows [heads, vdim, dim] float32 are read (unless
+    the request starts) and written."""
+    _require_cuda(work, o, state)
+    if work.dtype != torch.float32 or o.dtype != torch.float32 or state.dtype != torch.float32:
+        raise KernelError("gla_scan: work, o and state must be float32")
+    fn = _fn("gla", "fl_gla_scan", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p,
+                                    c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(fn(_ptr(work), _ld(work), _ptr(o), _ld(o), _ptr(state), state.stride(0), _ptr(step.req_start),
+              _ptr(step.req_ctx), _ptr(step.req_qlen), _ptr(step.req_slot), step.n_requests, heads, dim, vdim, _stream()),
+           "gla_scan")
+
+
+def gla_gated_norm(o, gate, weight, out, heads, vdim, eps):
+    """out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(gate[t, h]); weight [vdim] (or None) is shared by the heads."""
+    _require_cuda(o, gate, weight, out)
+    if gate.dtype != out.dtype or o.dtype != torch.float32:
+        raise KernelError("gla_gated_norm: gate and out share a dtype, o is float32")
+    fn = _fn("gla", "fl_gla_gated_norm", [c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_long, c_int,
+                                          c_int, c_int, c_float, c_void_p])
+    _check(fn(_ptr(o), _ld(o), _ptr(gate), dtype_code(gate), _ld(gate), _ptr(weight),
+              F32 if weight is None else dtype_code(weight), _ptr(out), _ld(out), out.shape[0], heads, vdim, float(eps),
+              _stream()), "gla_gated_norm")
 
 
 # ------------------------------------------------------------- routed experts
 
 def moe_pick(logits, bias, chosen, weights, top, softmax_scores=False, renormalise=False, groups=None, keep=None,
-             renormalise_eps=0.0):
+             renormalise_eps=0.0, group_top=1, weight_scale=1.0):
     """Per token, from the router's float32 logits [N, experts]: the `top` experts by score + bias (int32
     `chosen` [N, top]) and their scores (`weights`, divided by their sum + `renormalise_eps` with
     `renormalise`); scores are sigmoids, or a softmax over the experts.  With `groups` the experts form that
-    many equal groups of neighbours and only those of the `keep` groups with the largest best score + bias
-    can be chosen."""
+    many equal groups of neighbours and only those of the `keep` groups with the largest score can be chosen, a
+    group's score being the sum of its `group_top` largest score + bias (1: its best).  The weights are multiplied
+    by `weight_scale` at the end."""
     _require_cuda(logits, bias, chosen, weights)
     if logits.dtype != torch.float32 or chosen.shape[1] != top or not chosen.is_contiguous() or not weights.is_contiguous():
         raise KernelError("moe_pick: logits float32, chosen and weights contiguous [N, top]")
     fn = _fn("moe", "fl_moe_pick", [c_void_p, c_long, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                    c_int, c_int, c_int, c_float, c_void_p])
+                                    c_int, c_int, c_int, c_float, c_int, c_float, c_void_p])
     _check(fn(_ptr(logits), _ld(logits), _ptr(bias), F32 if bias is None else dtype_code(bias), _ptr(chosen),
               _ptr(weights), logits.shape[0], logits.shape[1], top, int(softmax_scores), int(renormalise),
-              int(groups or 1), int(keep or groups or 1), float(renormalise_eps), _stream()), "moe_pick")
+              int(groups or 1), int(keep or groups or 1), float(renormalise_eps), int(group_top), float(weight_scale),
+              _stream()), "moe_pick")
 
 
-def moe_experts(h, w_gate_up, w_down, chosen, weights, act_buf, out, activation="silu", params=(0.0, 0.0)):
+def moe_experts(h, w_gate_up, w_down, chosen, weights, act_buf, out, activation="silu", params=(0.0, 0.0), gated=True,
+                accumulate=False):
     """out[t] = sum_k weights[t, k] * down[e](f(gate[e] h[t], up[e] h[t])), e = chosen[t, k], f as in ACTIVATIONS;
-    w_gate_up [E, 2 ff, width], w_down [E, width, ff]; act_buf float32 [N * top, ff]."""
+    w_gate_up [E, 2 ff, width], w_down [E, width, ff]; act_buf float32 [N * top, ff].  Without a gate
+    (`gated=False`) w_gate_up is the up matrices alone, [E, ff, width], and the unit is f(up[e] h[t], 1).  With
+    `accumulate` the sum is added to what `out` holds."""
     _require_cuda(h, w_gate_up, w_down, chosen, weights, act_buf, out)
     experts, ff2, width = w_gate_up.shape
+    if not gated:
+        ff2 *= 2
     fn = _fn("moe", "fl_moe_experts", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                       c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+                                       c_void_p, c_long, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p])
     _check(fn(_ptr(h), dtype_code(h), _ld(h), _ptr(w_gate_up), _ptr(w_down), dtype_code(w_gate_up), _ptr(chosen),
               _ptr(weights), _ptr(act_buf), _ptr(out), _ld(out), h.shape[0], width, ff2 // 2, chosen.shape[1],
-              activation_code(activation), float(params[0]), float(params[1]), _stream()), "moe_experts", 2)
+              activation_code(activation), float(params[0]), float(params[1]), int(gated), int(accumulate), _stream()),
+           "moe_experts", 2)
 
 
 def moe_group_rows(n_tokens: int, top: int, experts: int) -> int:
@@ -820,19 +981,23 @@ def moe_group_takes(h_dtype, w_dtype, width: int, ff: int) -> bool:
     return bool(fn(_CODES[h_dtype], _CODES[w_dtype], width, ff))
 
 
-def moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, ints, act, y, out, activation="silu", params=(0.0, 0.0)):
+def moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, ints, act, y, out, activation="silu", params=(0.0, 0.0),
+                        gated=True, accumulate=False):
     """The same sum as `moe_experts` for many tokens: pairs ordered by expert, two tensor-core products
     over tiles of 64 rows, then the weighted sum per token.  All bfloat16; `ints` int32
     [rows + N * top + rows / 64 + 1], `act` bfloat16 [rows, ff], `y` float32 [rows, width] with
-    rows = moe_group_rows(N, top, experts)."""
+    rows = moe_group_rows(N, top, experts).  `gated=False`: as in `moe_experts`."""
     _require_cuda(h, w_gate_up, w_down, chosen, weights, ints, act, y, out)
     experts, ff2, width = w_gate_up.shape
+    if not gated:
+        ff2 *= 2
     fn = _fn("moe", "fl_moe_experts_grouped", [c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int,
-                                               c_int, c_float, c_float, c_void_p])
+                                               c_int, c_float, c_float, c_int, c_int, c_void_p])
     _check(fn(_ptr(h), _ld(h), _ptr(w_gate_up), _ptr(w_down), _ptr(chosen), _ptr(weights), _ptr(ints), _ptr(act),
               _ptr(y), _ptr(out), _ld(out), h.shape[0], width, ff2 // 2, chosen.shape[1], experts,
-              activation_code(activation), float(params[0]), float(params[1]), _stream()), "moe_experts_grouped", 4)
+              activation_code(activation), float(params[0]), float(params[1]), int(gated), int(accumulate), _stream()),
+           "moe_experts_grouped", 4)
 
 
 # -------------------------------------------------------------- rope + cache

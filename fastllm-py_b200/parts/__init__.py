@@ -1,4 +1,5 @@
-from . import attention, block, delta, differential, io, latent, mlp, moe, norm, retention, rotary, sink_attention  # noqa: F401  (registers the built-in parts)
+from . import (attention, block, delta, differential, gla, io, latent, mlp, moe, norm, normed_attention,  # noqa: F401
+               recurrence, retention, rotary, side_by_side, sink_attention)    # (registers the built-in parts)
 from .base import BuildContext, EngineLimits, Part, ResidualStream, Workspace
 from .decoder import Decoder
 from .plan import LayerRun, LayerSpec, ModelPlan, PartSpec

@@ -106,12 +106,22 @@ class ResidualStream:
         self.spill = spill           # a sublayer's output); a norm with `takes_post_norm` does both in one kernel
         self.extra = None            # a second tensor not yet added (a layer whose mixer and feed-forward run side by
                                      # side leaves two); a norm with `takes_extra` adds both while it reads
+        self.pending_scale = 1.0     # the pending sum is multiplied by this as it is added (a layer that scales its
+                                     # sublayers' results); a norm with `takes_scale` does so while it reads
+
+    def _add_scaled(self):
+        """x += pending_scale * pending (a tensor), for whoever cannot take the scale itself."""
+        from ..native import ops
+        ops.scaled_add(self.x, self.pending, self.pending_scale)
+        self.pending, self.pending_scale = None, 1.0
 
     def settle(self):
         """x takes in whatever is still pending (for a block whose sublayers read x itself)."""
         from ..native import ops
         if self.pending is not None and not isinstance(self.pending, torch.Tensor):
             self.pending = self.pending.reduce_into(self.spill())
+        if self.pending is not None and self.pending_scale != 1.0:
+            self._add_scaled()
         if self.pending is not None:
             if self.pending_norm is not None:
                 self.pending_norm.add_normed(self)
@@ -126,10 +136,13 @@ class ResidualStream:
         """`norm.apply(self, out, rows)`, with a pending sum that the norm can take."""
         pending = self.pending
         if pending is not None and not isinstance(pending, torch.Tensor):
-            both = getattr(norm, "takes_partial", False) and \
+            both = getattr(norm, "takes_partial", False) and self.pending_scale == 1.0 and \
                 (self.pending_norm is None or getattr(norm, "takes_post_norm", False))
             if rows is not None or not both:
                 pending = self.pending = pending.reduce_into(self.spill())
+        if pending is not None and self.pending_scale != 1.0 and not getattr(norm, "takes_scale", False):
+            self._add_scaled()                           # (every row, also when only some are normed)
+            pending = None
         if pending is not None and self.pending_norm is not None and not getattr(norm, "takes_post_norm", False):
             self.pending_norm.add_normed(self)           # x += norm(pending), for a norm that cannot do it itself
         if self.extra is not None and (not getattr(norm, "takes_extra", False) or self.pending_norm is not None

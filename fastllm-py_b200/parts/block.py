@@ -2,7 +2,8 @@
 
 "prenorm" is the Llama layer (fastllm_py/model.py:464-470):
     x = x + mixer(norm_mixer(x));  x = x + feed_forward(norm_ff(x))
-The sums are left pending on the residual stream and folded into the next norm.
+The sums are left pending on the residual stream and folded into the next norm.  With `residual_scale`
+m both sums are multiplied by m as they are added, and the layer may have no feed-forward.
 
 "sandwich" norms each sublayer on both sides:
     x = x + norm_mixer_out(mixer(norm_mixer_in(x)));  x = x + norm_ff_out(ff(norm_ff_in(x)))
@@ -24,19 +25,25 @@ from .registry import build_part, register_part
 
 @register_part("block", "prenorm")
 class PreNormBlock(Part):
-    """norm roles: "mixer", "feed_forward"."""
+    """norm roles: "mixer" and, with a feed-forward, "feed_forward".  params: residual_scale (1)."""
     category = "block"
 
     def __init__(self, layer_spec, ctx):
         super().__init__(layer_spec, ctx)
         self.mixer = build_part("mixer", layer_spec.mixer, ctx)
-        self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, ctx)
         self.norm_mixer = build_part("norm", layer_spec.norms["mixer"], ctx)
-        self.norm_ff = build_part("norm", layer_spec.norms["feed_forward"], ctx)
+        self.feed_forward = self.norm_ff = None
+        if layer_spec.feed_forward is not None:
+            self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, ctx)
+            self.norm_ff = build_part("norm", layer_spec.norms["feed_forward"], ctx)
         self.hidden = self.norm_mixer.size
+        self.scale = float(layer_spec.params.get("residual_scale", 1.0))
 
     def children(self):
-        return [self.mixer, self.feed_forward, self.norm_mixer, self.norm_ff]
+        parts = [self.mixer, self.norm_mixer]
+        if self.feed_forward is not None:
+            parts += [self.feed_forward, self.norm_ff]
+        return parts
 
     def forward(self, stream, step, cache):
         n = stream.x.shape[0]
@@ -47,10 +54,12 @@ class PreNormBlock(Part):
         # split-K partial sums of its last product, which the next norm adds up
         stream.norm_into(self.norm_mixer, h)
         left = self.mixer.forward(h, delta, step, cache)
-        stream.pending = delta if left is None else left
+        stream.pending, stream.pending_scale = (delta if left is None else left), self.scale
+        if self.feed_forward is None:
+            return
         stream.norm_into(self.norm_ff, h)
         left = self.feed_forward.forward(h, delta, step)
-        stream.pending = delta if left is None else left
+        stream.pending, stream.pending_scale = (delta if left is None else left), self.scale
 
 
 @register_part("block", "sandwich")

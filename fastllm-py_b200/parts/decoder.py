@@ -28,6 +28,7 @@ class Decoder:
         self.final_norm = build_part("norm", plan.final_norm, ctx)
         self.head = build_part("head", plan.head, ctx)
         self.order = list(plan.order)
+        self.observer = None
         for i, run in enumerate(self.order):
             need = self.blocks[run.layer].mixer.cache_need()
             if run.cache is not None and need is not None:
@@ -97,15 +98,19 @@ class Decoder:
     EMBEDDING_STATE = "embedding"        # cache id of the embedding part's per-request state
 
     def cache_needs(self) -> dict:
-        """cache id -> need: the run index for the runs whose mixer owns a cache or a state; ("block", run index)
+        """cache id -> need: the run index for the runs whose mixer owns a cache or a state; (run index, name) for
+        each need of a mixer that has several (`cache_needs()`: mixers side by side); ("block", run index)
         for a block arrangement with per-request state of its own (`state_need()`); `EMBEDDING_STATE` for an
         embedding part with one."""
         needs = {}
         for i, run in enumerate(self.order):
             if run.cache is None:
-                need = self.blocks[run.layer].mixer.cache_need()
+                mixer = self.blocks[run.layer].mixer
+                need = mixer.cache_need()
                 if need is not None:
                     needs[i] = need
+                for name, sub in (mixer.cache_needs() if hasattr(mixer, "cache_needs") else {}).items():
+                    needs[(i, name)] = sub
             fn = getattr(self.blocks[run.layer], "state_need", None)
             need = fn() if fn is not None else None
             if need is not None:
@@ -184,10 +189,14 @@ class Decoder:
             cache_id = i if run.cache is None else run.cache
             block = self.blocks[run.layer]
             cache = step.cache_view(cache_id, run.cache is None)
+            if hasattr(block.mixer, "cache_needs"):            # several caches or states: the views by name
+                cache = {name: step.cache_view((cache_id, name), run.cache is None) for name in block.mixer.cache_needs()}
             if hasattr(block, "state_need"):
                 block.forward(stream, step, cache, step.cache_view(("block", i), True))
             else:
                 block.forward(stream, step, cache)
+            if self.observer is not None:                      # (a debugging aid: sees the stream after every run,
+                self.observer(i, stream)                       # with the run's last sum still pending)
         m = step.n_wanted
         logits = ws.rows("logits", m, self.vocab, torch.float32, initial=64)
         if m > 0:

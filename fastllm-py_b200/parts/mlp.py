@@ -61,3 +61,41 @@ class SwiGLU(Part):
         else:
             ops.swiglu_partial(partial, act)
         return self.down.forward(act, out, defer=True)
+
+
+@register_part("feed_forward", "mlp")
+class PlainMLP(Part):
+    """A feed-forward without a gate: down(act(up(h))), no biases; act is the gated units' f(x, 1)
+    (`native.ops.ACTIVATIONS`: "relu_squared" is relu(x)^2).
+    params: hidden_size, intermediate_size, activation ("relu_squared"), activation_params ((0, 0)).
+    tensors: up [I, hidden], down [hidden, I]."""
+    category = "feed_forward"
+    native_libraries = ("norm_mix",)
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.activation = spec.params.get("activation", "relu_squared")
+        ops.activation_code(self.activation)
+        self.activation_params = tuple(float(v) for v in spec.params.get("activation_params", (0.0, 0.0)))
+        self.up = self.down = None
+
+    def weight_shapes(self):
+        return {"up": (self.inter, self.hidden), "down": (self.hidden, self.inter)}
+
+    def load(self, tensors):
+        self.up = Linear([tensors["up"]])
+        self.down = Linear([tensors["down"]])
+
+    def reserve(self, limits):
+        for lin in (self.up, self.down):
+            if lin is not None:
+                lin.reserve(self.ctx.dtype, limits.max_tokens)
+
+    def forward(self, h, out, step):
+        n = h.shape[0]
+        act = step.workspace.rows("mlp_act", n, self.inter, self.ctx.dtype)
+        self.up.forward(h, act)
+        ops.activation(act, act, self.activation, self.activation_params)
+        return self.down.forward(act, out, defer=True)

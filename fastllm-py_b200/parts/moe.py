@@ -6,11 +6,14 @@ Router: logits z = W_r h in float; scores s = sigmoid(z) (`score`: "sigmoid" or
 chosen, where the bias (`correction`, a stored vector) steers the choice only;
 the weights are the chosen experts' s, divided by their sum (+ `renormalise_eps`)
 only if `renormalise` says so.  With `groups`, the experts form that many equal
-groups of neighbours, a group's score is the largest s + bias in it, and only
-experts of the `keep_groups` best groups can be chosen.  Expert e:
+groups of neighbours, a group's score is the sum of the `group_top` largest s + bias
+in it (1: the largest), and only experts of the `keep_groups` best groups can be
+chosen.  The weights are multiplied by `weight_scale` at the end.  Expert e:
 W_down,e f(W_gate,e h, W_up,e h) with f = act(g) * u or the clamped swish unit
-(`native.ops.ACTIVATIONS`), no biases.  The experts' matrices are stacked at load into [experts, 2 ff, hidden]
-(gate rows, then up rows) and [experts, hidden, ff].
+(`native.ops.ACTIVATIONS`), no biases; without a gate (`gated` False) W_down,e f(W_up,e h, 1).
+The experts' matrices are stacked at load into [experts, 2 ff, hidden]
+(gate rows, then up rows; [experts, ff, hidden] without a gate) and [experts, hidden, ff].
+A `shared` feed-forward part runs for every token and is added to the experts' sum.
 
 Two ways through the experts.  Few tokens (decode steps): one launch over
 (token, choice) pairs, each streaming its expert's rows; the matrices are read
@@ -26,16 +29,17 @@ import torch
 from ..native import ops, scratch
 from .base import Part
 from .linear import Linear
-from .registry import register_part
+from .registry import build_part, register_part
 
 
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(Part):
     """params: hidden_size, experts, top, expert_ff, activation ("silu"), activation_params ((0, 0)), score ("sigmoid"),
-    renormalise (False), renormalise_eps (0), groups (None), keep_groups (None: all),
+    renormalise (False), renormalise_eps (0), groups (None), keep_groups (None: all), group_top (1),
+    weight_scale (1), gated (True), shared (None | PartSpec of a feed-forward),
     choice_bias (True: a `correction` tensor is added to the scores for the choice).
     tensors: router [experts, hidden], correction [experts] (if choice_bias), and per expert i
-    gate.i, up.i [ff, hidden], down.i [hidden, ff]."""
+    gate.i (if gated), up.i [ff, hidden], down.i [hidden, ff]."""
     category = "feed_forward"
     native_libraries = ("moe",)
     GROUP_FROM = 128                 # (token, choice) pairs from which the grouped path is taken
@@ -52,6 +56,10 @@ class RoutedExperts(Part):
         self.groups = p.get("groups")
         self.keep_groups = p.get("keep_groups") or self.groups
         self.renormalise_eps = float(p.get("renormalise_eps", 0.0))
+        self.group_top = int(p.get("group_top", 1))
+        self.weight_scale = float(p.get("weight_scale", 1.0))
+        self.gated = bool(p.get("gated", True))
+        self.shared = build_part("feed_forward", p["shared"], ctx) if p.get("shared") is not None else None
         self.score = p.get("score", "sigmoid")
         if self.score not in ("sigmoid", "softmax"):
             raise ValueError(f"routed_experts: score {self.score!r} is not 'sigmoid' or 'softmax'")
@@ -66,12 +74,16 @@ class RoutedExperts(Part):
         if self.hidden * 4 > 48 * 1024:
             raise ValueError(f"routed_experts: hidden size {self.hidden} exceeds the kernels' 12288")
 
+    def children(self):
+        return [self.shared] if self.shared is not None else []
+
     def weight_shapes(self):
         shapes = {"router": (self.experts, self.hidden)}
         if self.choice_bias:
             shapes["correction"] = (self.experts,)
         for e in range(self.experts):
-            shapes[f"gate.{e}"] = (self.ff, self.hidden)
+            if self.gated:
+                shapes[f"gate.{e}"] = (self.ff, self.hidden)
             shapes[f"up.{e}"] = (self.ff, self.hidden)
             shapes[f"down.{e}"] = (self.hidden, self.ff)
         return shapes
@@ -79,12 +91,14 @@ class RoutedExperts(Part):
     def load(self, tensors):
         self.router = Linear([tensors["router"]])
         self.correction = tensors["correction"].contiguous() if self.choice_bias else None
-        first = tensors["gate.0"]
-        self.gate_up = torch.empty((self.experts, 2 * self.ff, self.hidden), dtype=first.dtype, device=first.device)
+        first = tensors["up.0"]
+        rows = 2 * self.ff if self.gated else self.ff
+        self.gate_up = torch.empty((self.experts, rows, self.hidden), dtype=first.dtype, device=first.device)
         self.down = torch.empty((self.experts, self.hidden, self.ff), dtype=first.dtype, device=first.device)
         for e in range(self.experts):                    # expert by expert: no second copy of all of them
-            self.gate_up[e, :self.ff] = tensors[f"gate.{e}"]
-            self.gate_up[e, self.ff:] = tensors[f"up.{e}"]
+            if self.gated:
+                self.gate_up[e, :self.ff] = tensors[f"gate.{e}"]
+            self.gate_up[e, rows - self.ff:] = tensors[f"up.{e}"]
             self.down[e] = tensors[f"down.{e}"]
 
     def _grouped(self, dtype) -> bool:
@@ -103,6 +117,7 @@ class RoutedExperts(Part):
 
     def reserve(self, limits):
         self.router.reserve(self.ctx.dtype, limits.max_tokens)
+
         if self.ctx.device.type == "cuda" and self._grouped(self.ctx.dtype):
             self._group_buffers(limits.max_tokens, self.ctx.device)       # sized now: nothing grows under a graph
 
@@ -116,12 +131,18 @@ class RoutedExperts(Part):
         logits = ws.rows("moe_logits", n, self.experts, torch.float32)
         self.router.forward(h, logits)                       # float accumulation, float logits
         ops.moe_pick(logits, self.correction, chosen, weights, self.top, self.score == "softmax", self.renormalise,
-                     self.groups, self.keep_groups, self.renormalise_eps)
+                     self.groups, self.keep_groups, self.renormalise_eps, self.group_top, self.weight_scale)
+        shared = self.shared is not None
+        if shared:                                           # the shared unit first: the experts' sum is added to it
+            left = self.shared.forward(h, out, step)
+            if left is not None:
+                left.reduce_into(out)
         if n * self.top >= self.GROUP_FROM and self._grouped(h.dtype):
             ints, act, y = self._group_buffers(n, h.device)
             ops.moe_experts_grouped(h, self.gate_up, self.down, chosen, weights, ints, act, y, out, self.activation,
-                                    self.activation_params)
-            return None
-        act = ws.rows("moe_act", n, self.top * self.ff, torch.float32)
-        ops.moe_experts(h, self.gate_up, self.down, chosen, weights, act, out, self.activation, self.activation_params)
+                                    self.activation_params, self.gated, accumulate=shared)
+        else:
+            act = ws.rows("moe_act", n, self.top * self.ff, torch.float32)
+            ops.moe_experts(h, self.gate_up, self.down, chosen, weights, act, out, self.activation, self.activation_params,
+                            self.gated, accumulate=shared)
         return None

@@ -80,6 +80,41 @@ class RMSNorm(Part):
         stream.pending = stream.extra = None
 
 
+@register_part("norm", "layernorm")
+class LayerNorm(Part):
+    """(x - mean) / sqrt(var + eps) * weight + bias, the variance being the mean of the squared deviations.
+    params: size, eps, bias (True).  tensors: weight [size] and, with bias, bias [size].  Adds the stream's pending
+    sum, multiplied by the stream's `pending_scale`, while it reads."""
+    category = "norm"
+    native_libraries = ("norm_mix",)
+    takes_scale = True                   # the pending sum times a number: added while the row is read
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.has_bias = bool(spec.params.get("bias", True))
+        self.weight = self.bias = None
+
+    def weight_shapes(self):
+        shapes = {"weight": (self.size,)}
+        if self.has_bias:
+            shapes["bias"] = (self.size,)
+        return shapes
+
+    def load(self, tensors):
+        self.weight = tensors["weight"].contiguous()
+        if self.has_bias:
+            self.bias = tensors["bias"].to(self.weight.dtype).contiguous()
+
+    def apply(self, stream, out, rows=None):
+        """Norm the residual stream into `out`, adding the pending sum (a tensor: `ResidualStream.norm_into` sees to
+        it) first.  With `rows` only those rows are normed, into out[0..m), and the pending sum stays pending."""
+        ops.add_layernorm(stream.x, stream.pending, stream.pending_scale, self.weight, self.bias, out, self.eps, rows)
+        if rows is None:
+            stream.pending, stream.pending_scale = None, 1.0
+
+
 @register_part("norm", "rmsnorm_scalar")
 class ScalarRMSNorm(RMSNorm):
     """RMSNorm whose weight is ONE stored number g for all coordinates: x * (mean(x^2) + eps)^-1/2 * g.

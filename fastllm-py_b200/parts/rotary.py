@@ -15,6 +15,11 @@ d(t) = D ln(original / (2 pi t)) / (2 ln theta); lo = max(floor(d(fast)), 0), hi
 ramp_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1); the frequency is
 inv_freq[j] * ((1 - ramp_j) + ramp_j / factor), and cos and sin are both multiplied by
 0.1 ln(factor) + 1.
+
+Scaling by bands of wavelength ("bands": factor, original, low, high): a pair whose wavelength
+2 pi / inv_freq is shorter than original / high keeps its frequency, one longer than
+original / low turns `factor` times slower, and between the two the frequency is
+(1 - s) inv_freq / factor + s inv_freq with s = (original / wavelength - low) / (high - low).
 """
 from __future__ import annotations
 
@@ -28,7 +33,7 @@ from .registry import register_part
 @register_part("position", "rotary")
 class Rotary(Part):
     """params: rot_dim (even, <= head_dim), theta, scaling: None | ("linear", factor) | ("yarn", factor, original,
-    fast, slow), exact (False: the
+    fast, slow) | ("bands", factor, original, low, high), exact (False: the
     frequencies and angles are rounded to float32 before cos and sin, as above; True: they are formed in
     float64 and only cos and sin are rounded, for models specified by the formula rather than by float32 code)."""
     category = "position"
@@ -41,9 +46,9 @@ class Rotary(Part):
         self.exact = bool(spec.params.get("exact", False))
         if self.rot_dim % 2:
             raise ValueError(f"rotary: rot_dim {self.rot_dim} must be even")
-        if self.scaling is not None and self.scaling[0] not in ("linear", "yarn"):
+        if self.scaling is not None and self.scaling[0] not in ("linear", "yarn", "bands"):
             raise ValueError(f"rotary: scaling {self.scaling[0]!r} is not supported")
-        if self.scaling is not None and self.scaling[0] == "yarn" and not self.exact:
+        if self.scaling is not None and self.scaling[0] in ("yarn", "bands") and not self.exact:
             raise ValueError("rotary: blended scaling is formed in float64 (exact=True)")
 
     def tables(self):
@@ -65,6 +70,13 @@ class Rotary(Part):
                 ramp = np.clip((np.arange(d // 2, dtype=np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
                 inv_freq = inv_freq / factor * ramp + inv_freq * (1.0 - ramp)
                 gain = 0.1 * np.log(factor) + 1.0
+            elif self.scaling is not None and self.scaling[0] == "bands":
+                factor, original, low, high = (float(v) for v in self.scaling[1:])
+                wave = 2.0 * np.pi / inv_freq
+                s = (original / wave - low) / (high - low)
+                inv_freq = np.where(wave < original / high, inv_freq,
+                                    np.where(wave > original / low, inv_freq / factor,
+                                             (1.0 - s) * inv_freq / factor + s * inv_freq))
             elif self.scaling is not None:
                 pos = pos / float(self.scaling[1])
             ang = pos[:, None] * inv_freq[None, :]

@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl ours|reference]
-                    [--workload decode|serve|67b|tables|hybrid|lasonex|sakusun]
+                    [--workload decode|serve|67b|tables|hybrid|lasonex|sakusun|saberax]
 
 The default run is the DeepSeek-LLM-7B sized model (30 layers, hidden 4096,
 32 heads, head size 128, feed-forward 11008, vocabulary 102400) with random
@@ -46,6 +46,8 @@ Two more workloads, each printing one line of its own:
                      at the same two widths, beside the Tigitar hybrid and the dense decoder
   --workload sakusun the Sakusun design (windowed sink attention + latent attention in gated post-norm layers with an
                      input convolution) at the same two widths, beside the Tigitar hybrid and the dense decoder
+  --workload saberax the Saberax design (attention beside a gated recurrence or gated linear attention in pre-norm layers,
+                     chunked attention, experts without a gate) beside the Lasonex design and the dense decoder
   --workload 67b     deepseek-llm-67b size (95 layers, hidden 8192, 64 heads over 8 key/value
              heads; 135 GB of weights on the one GPU): a 2048-token prompt step and decode
              steps at batch 1, 8 and 16 with 4000-token contexts, with their roofline fractions.
@@ -940,6 +942,168 @@ def run_sakusun(args, warmup):
     return 0
 
 
+SABERAX_SIZES = {
+    # pre-norm layers of attention beside a recurrent mixer at the widths of HYBRID_SIZES; layers cycle through
+    # attention + recurrent unit with a dense unit, windowed attention + gated linear attention with routed experts,
+    # the same with a dense unit, chunked attention with routed experts.  The Lasonex design (windowed attention and a
+    # linear-attention state in parallel layers, grouped experts) and the dense Llama-style decoder of the same width
+    # and depth are timed beside it
+    "w2048": dict(width=2048, vocab=32256, layers=8, attention=dict(heads=16, kv_heads=4, dim=128, vdim=128, window=1024),
+                  recurrent=dict(width=2048, blocks=8, conv=4), linear=dict(heads=16, dim=64, vdim=128, tau=16.0),
+                  dense_ff=5504, experts=32, top=4, expert_ff=1408, shared_ff=1408, groups=(8, 4)),
+    "w4096": dict(width=4096, vocab=32256, layers=4, attention=dict(heads=32, kv_heads=8, dim=128, vdim=128, window=2048),
+                  recurrent=dict(width=4096, blocks=16, conv=4), linear=dict(heads=32, dim=64, vdim=128, tau=16.0),
+                  dense_ff=11008, experts=16, top=2, expert_ff=5504, shared_ff=5504, groups=(4, 2)),
+}
+
+
+def saberax_config(size):
+    from fastllm_py_b200.config.saberax import (AttentionConfig, DenseConfig, ExpertsConfig, GatedLinearAttentionConfig,
+                                                PairConfig, RecurrentUnitConfig, RotationConfig, SaberaxConfig,
+                                                SaberaxLayerConfig)
+
+    z = SABERAX_SIZES[size]
+    a, r, g = z["attention"], z["recurrent"], z["linear"]
+    sizes = (a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["dim"] ** -0.5)
+    normed = AttentionConfig("normed", *sizes, None, None, (0.3, 128))
+    windowed = AttentionConfig("windowed", *sizes, a["window"], RotationConfig(10000.0, 64, ("yarn", 4.0, 4096.0, 32.0, 1.0)), None)
+    chunked = AttentionConfig("chunked", *sizes, a["window"], RotationConfig(250000.0, a["dim"], ("bands", 4.0, 2048.0, 1.0, 4.0)), None)
+    first = PairConfig(normed, RecurrentUnitConfig(r["width"], r["blocks"], r["conv"]))
+    second = PairConfig(windowed, GatedLinearAttentionConfig(g["heads"], g["dim"], g["vdim"], g["tau"]))
+    dense = DenseConfig(z["dense_ff"])
+    routed = ExpertsConfig(z["experts"], z["top"], 2.0, z["groups"][0], z["groups"][1], z["expert_ff"], z["shared_ff"])
+    cycle = [("parallel", first, dense), ("parallel_2", second, routed), ("parallel_2", second, dense), ("attention", chunked, routed)]
+    layers = tuple(SaberaxLayerConfig(*cycle[i % 4], None) for i in range(z["layers"]))
+    return SaberaxConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-5, residual_mult=0.7, layers=layers)
+
+
+def _saberax_layer_sizes(layer, w):
+    """(weight elements a token's mixer products touch, state floats per request, [(attention config, reach)])."""
+    from fastllm_py_b200.config.saberax import AttentionConfig, GatedLinearAttentionConfig, RecurrentUnitConfig
+
+    def attention(m):
+        v = 0 if m.role == "chunked" else m.kv_heads * m.vdim
+        return w * (m.heads * m.dim + m.kv_heads * m.dim + v + m.heads * m.vdim + (m.heads if m.role == "chunked" else 0))
+
+    m = layer.mixer
+    if isinstance(m, AttentionConfig):
+        return attention(m), 0, [m]
+    weights, state = attention(m.left), 0
+    r = m.right
+    if isinstance(r, RecurrentUnitConfig):
+        weights += 3 * w * r.width + 2 * r.width * (r.width // r.blocks)
+        state = r.width * r.conv
+    elif isinstance(r, GatedLinearAttentionConfig):
+        weights += w * (2 * r.heads * r.dim + 3 * r.heads * r.vdim + r.rank) + r.heads * r.dim * r.rank
+        state = r.heads * r.dim * r.vdim
+    return weights, state, [m.left]
+
+
+def saberax_decode_bytes(cfg, batch, context):
+    """Bytes a decode step has to move: the weights it uses once in bfloat16 (of the experts, those that `batch`
+    tokens can reach), every request's recurrent states read and written in float, and the cache rows that each
+    attention sees (all of them, the window's, or on average half a chunk's)."""
+    from fastllm_py_b200.config.saberax import ExpertsConfig
+
+    w, total = cfg.width, 0
+    for layer in cfg.layers:
+        weights, state, attentions = _saberax_layer_sizes(layer, w)
+        total += 2 * weights + batch * 2 * 4 * state
+        for m in attentions:
+            seen = context if m.mask is None else min(context, m.mask) / (2 if m.role == "chunked" else 1)
+            total += batch * seen * m.kv_heads * (m.dim + m.vdim) * 2
+        f = layer.mlp
+        if isinstance(f, ExpertsConfig):
+            total += 2 * 2 * w * f.ff * min(f.experts, batch * f.top) + 2 * w * f.experts + 2 * 2 * w * (f.shared_ff or 0)
+        elif f is not None:
+            total += 2 * 3 * w * f.ff
+    return total + 2 * w * cfg.vocab + 2 * batch * w
+
+
+def saberax_prefill_flops(cfg, tokens):
+    """Matrix-product FLOPs of a prompt step (projections, gates of the recurrent unit, feed-forwards, attention over what
+    each query sees, head); the linear attention's recurrence adds 4 dim vdim per head and token."""
+    from fastllm_py_b200.config.saberax import ExpertsConfig, GatedLinearAttentionConfig, PairConfig
+
+    w, total = cfg.width, 0
+    for layer in cfg.layers:
+        weights, _, attentions = _saberax_layer_sizes(layer, w)
+        total += 2 * tokens * weights
+        if isinstance(layer.mixer, PairConfig) and isinstance(layer.mixer.right, GatedLinearAttentionConfig):
+            r = layer.mixer.right
+            total += tokens * r.heads * 4 * r.dim * r.vdim
+        for m in attentions:
+            if m.role == "chunked" and m.mask:
+                seen = sum(p % m.mask + 1 for p in range(tokens))
+            else:
+                seen = sum(min(p + 1, m.mask or p + 1) for p in range(tokens))
+            total += 2 * m.heads * seen * (m.dim + m.vdim)
+        f = layer.mlp
+        if isinstance(f, ExpertsConfig):
+            total += 2 * tokens * (2 * w * f.ff * f.top + w * f.experts + 2 * w * (f.shared_ff or 0))
+        elif f is not None:
+            total += 2 * tokens * 3 * w * f.ff
+    return total + 2 * w * cfg.vocab
+
+
+def run_saberax(args, warmup):
+    """The Saberax design beside the Lasonex design (the closest model: windowed attention and a recurrent state side
+    by side in every layer, grouped experts) and the dense decoder of equal width and depth, one JSON line: prompt steps
+    of 512 and 2048 tokens and decode steps at batch 1 and 8 over 2048-token contexts, with each model's fraction of its
+    own roofline (measured tensor peak for prompts, measured copy bandwidth for decode steps)."""
+    from fastllm_py_b200 import LlamaConfig, Model
+
+    pk = peaks()
+    steps = max(8, min(args.steps, 32))
+    out = {}
+    sampler = ClockSampler().start()
+    sampler.__enter__()
+    for size in (args.size.split(",") if args.size else list(SABERAX_SIZES)):
+        z, hz = SABERAX_SIZES[size], HYBRID_SIZES[size]
+        llama = LlamaConfig(architecture="LlamaForCausalLM", rope_scaling=None, tie_word_embeddings=False,
+                            num_layers=z["layers"], hidden_size=z["width"], vocab_size=z["vocab"], rope_theta=10000.0,
+                            rms_norm_eps=1e-6, max_position_embeddings=4096, **hz["llama"])
+        models = [("saberax", saberax_config(size), saberax_prefill_flops, saberax_decode_bytes),
+                  ("lasonex", lasonex_config(size), lasonex_prefill_flops, lasonex_decode_bytes),
+                  ("dense", llama, prefill_flops, decode_bytes)]
+        res = {}
+        for name, cfg, flops_of, bytes_of in models:
+            if args.only and name not in args.only.split(","):
+                continue
+            model = Model.from_config(cfg, seed=0, dtype="bfloat16", page_size=16, max_tokens=8 * (CONTEXT + 256),
+                                      max_requests=8, max_batched_tokens=2048, max_model_len=4096,
+                                      cuda_graph=not args.no_graph)
+            r = {"prompt_step": {}, "decode": {}}
+            for t in (512, 2048):
+                ms, _ = time_prefill(model, t, 8, 3)
+                r["prompt_step"][str(t)] = {"ms": round(ms, 3), "value": round(t * 1000.0 / ms, 1),
+                                            "frac": round(flops_of(cfg, t) / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+            for b in (1, 8):
+                v, ms, launches, _ = time_decode(model, b, steps, warmup, CONTEXT)
+                ctx = CONTEXT + warmup + (steps + 1) / 2
+                r["decode"][f"{b}x{CONTEXT}"] = {"ms_per_step": round(ms, 3), "value": round(v, 1),
+                                                 "launches_per_step": launches // steps,
+                                                 "frac": round(bytes_of(cfg, b, ctx) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+            res[name] = r
+            del model
+            import gc
+
+            import torch
+            gc.collect()
+            torch.cuda.empty_cache()
+        out[size] = res
+    sampler.__exit__()
+    print(json.dumps({
+        "metric": "prompt and decode steps of the Saberax design beside the Lasonex design and the dense decoder "
+                  "of equal size, bf16",
+        "n_gpus": 1, "dtype": "bf16", "data": "synthetic", "impl": "ours", "steps": steps, "warmup": warmup,
+        "config": {"sizes": {k: dict(SABERAX_SIZES[k]) for k in out}, "page_size": 16,
+                   "peaks": pk["source"], "hbm_gbs": pk["hbm_gbs"], "bf16_tflops": pk["bf16_tflops"],
+                   "cuda_graph": not args.no_graph},
+        "sizes": out, "clocks": sampler.summary()}))
+    return 0
+
+
 def reference_cpu_path(ref_root, layers=1, context=256, decode_tokens=8):
     """fastllm-py's own NumPy model code (its CPU device, float32) timed at DeepSeek-LLM-7B layer
     sizes: `layers` of the 30 layers, one sequence (that path has no batch), a `context`-token
@@ -1076,11 +1240,11 @@ def main():
                     help="run fewer layers of the same sizes (the line names both numbers)")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and the prefill")
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "67b", "tables", "hybrid", "lasonex", "sakusun"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serve", "67b", "tables", "hybrid", "lasonex", "sakusun", "saberax"],
                     help="decode: the headline line (DeepSeek-LLM-7B size); serve: continuous batching at "
                          "deepseek-coder-1.3b size; 67b: prompt and decode steps at deepseek-llm-67b size")
-    ap.add_argument("--size", default="", help="hybrid, lasonex, sakusun: which sizes (w2048,w4096; default both)")
-    ap.add_argument("--only", default="", help="lasonex, sakusun: which of the models timed side by side (lasonex or sakusun, hybrid, dense)")
+    ap.add_argument("--size", default="", help="hybrid, lasonex, sakusun, saberax: which sizes (w2048,w4096; default both)")
+    ap.add_argument("--only", default="", help="lasonex, sakusun, saberax: which of the models timed side by side (the design itself, hybrid or lasonex, dense)")
     ap.add_argument("--requests", type=int, default=128, help="serve: how many requests")
     ap.add_argument("--rate", type=float, default=16.0, help="serve: mean arrivals a second")
     ap.add_argument("--reference-cpu", action="store_true",
@@ -1103,6 +1267,8 @@ def main():
         return run_lasonex(args, warmup)
     if args.workload == "sakusun":
         return run_sakusun(args, warmup)
+    if args.workload == "saberax":
+        return run_saberax(args, warmup)
     if args.workload == "hybrid":
         return run_hybrid(args, warmup)
     args.layers = args.layers or MODEL_7B["num_layers"]

@@ -16,7 +16,8 @@ config.json is nested:
     mixer of "attention" (keys serve as values; a query sees its own chunk of positions; a sink; a gate per head):
         heads, kv_heads, dim, vdim, scale, mask {size} (absent: every earlier token),
         rot {base, dims, scaling {factor, low, high, original} (absent: none)} (absent: no rotation)
-    mixer of "parallel":  left  {heads, kv_heads, dim, vdim, scale, q_temp {coef, every} (absent: none)}
+    mixer of "parallel":  left  {heads, kv_heads, dim, vdim, scale, q_temp {coef, every} (absent: none),
+                                 mask {size} (a window; absent: every earlier token)}
                           right {width, blocks, conv}
     mixer of "parallel_2": left {heads, kv_heads, dim, vdim, scale, mask {size} (absent: every earlier token),
                                  rot {base, dims, scaling {factor, original, fast, slow} (absent: none)}}

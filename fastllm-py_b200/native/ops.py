@@ -861,12 +861,15 @@ def activation(x, out, name: str, params=(0.0, 0.0)):
 
 # ---------------------------------------------- gated recurrence per channel
 
-def rglru(proj, bias, conv_w, conv_b, w_a, w_i, b_a, b_i, rate, state, step, u, a, bx, out, width, blocks, taps):
+def rglru(proj, bias, conv_w, conv_b, w_a, w_i, b_a, b_i, rate, state, step, u, a, bx, out, width, blocks, taps,
+          fixed_order=False):
     """The gated linear recurrence per channel over the step's tokens.  proj [N, 2 width] = gate branch | input branch
     before their biases (`bias`, float32 [2 width]); the input branch passes a causal convolution (`conv_w`
     [width, taps], `conv_b`), the gates r and i are sigmoids of block-diagonal products of it (`w_a`, `w_i`
     [blocks, width / blocks, width / blocks], `b_a`, `b_i` [width]), a = exp(rate * r), S <- a S + sqrt(1 - a^2) i u;
-    out = S * gelu_tanh(gate branch).  state rows: [S | the last taps - 1 inputs] float32; u, a, bx: float32 [N, width]."""
+    out = S * gelu_tanh(gate branch).  state rows: [S | the last taps - 1 inputs] float32; u, a, bx: float32 [N, width].
+    `fixed_order`: the recurrence runs token by token whatever the step's shape (otherwise a prompt portion's tokens run
+    in segments side by side, and the sums' order follows the cut)."""
     _require_cuda(proj, bias, conv_w, conv_b, w_a, w_i, b_a, b_i, rate, state, u, a, bx, out)
     for v in (bias, conv_w, conv_b, b_a, b_i, rate, state, u, a, bx):
         if v.dtype != torch.float32:
@@ -878,12 +881,12 @@ def rglru(proj, bias, conv_w, conv_b, w_a, w_i, b_a, b_i, rate, state, step, u, 
     fn = _fn("rglru", "fl_rglru", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_long, c_int,
-                                   c_int, c_int, c_void_p])
+                                   c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(bias), _ptr(conv_w), _ptr(conv_b), _ptr(w_a), _ptr(w_i),
               dtype_code(w_a), _ptr(b_a), _ptr(b_i), _ptr(rate), _ptr(state), state.stride(0), _ptr(step.tok_req),
               _ptr(step.positions), _ptr(step.req_start), _ptr(step.req_ctx), _ptr(step.req_qlen), _ptr(step.req_slot),
               proj.shape[0], step.n_requests, _ptr(u), _ptr(a), _ptr(bx), _ld(u), _ptr(out), _ld(out), width, blocks, taps,
-              _stream()), "rglru", 3)
+              int(fixed_order), _stream()), "rglru", 3)
 
 
 # ---------------------------------------------------- gated linear attention

@@ -40,8 +40,8 @@ class GatedRecurrence(Part):
             raise ValueError(f"gated_recurrence: {self.blocks} blocks do not divide the width {self.width}")
         if not 1 <= self.taps <= 16:
             raise ValueError(f"gated_recurrence: {self.taps} taps are beyond the kernels' 16")
-        if (self.width // self.blocks) * 8 * 4 > 48 * 1024:
-            raise ValueError(f"gated_recurrence: blocks of {self.width // self.blocks} channels exceed the kernel's 1536")
+        if (self.width // self.blocks) * 16 * 4 > 48 * 1024:
+            raise ValueError(f"gated_recurrence: blocks of {self.width // self.blocks} channels exceed the kernel's 768")
         self.proj = self.o = None
 
     def cache_need(self):
@@ -84,5 +84,6 @@ class GatedRecurrence(Part):
         bx = ws.rows("recurrence_bx", n, self.width, torch.float32)
         gated = ws.rows("recurrence_out", n, self.width, dt)
         ops.rglru(proj, self.bias, self.conv_w, self.conv_b, self.gate_a, self.gate_i, self.gate_a_bias, self.gate_i_bias,
-                  self.rate_c, cache.tensor, step, u, a, bx, gated, self.width, self.blocks, self.taps)
+                  self.rate_c, cache.tensor, step, u, a, bx, gated, self.width, self.blocks, self.taps,
+                  fixed_order=dt == torch.float32)        # the 32-bit path: cuts and batches agree bit for bit
         return self.o.forward(gated, out, defer=True)

@@ -105,8 +105,8 @@ def softmax_attention(q, k, v, scale, visible, sink=None):
 
 
 def qk_normed_attention(h, t, m, eps, alter=()):
-    """Causal softmax attention without rotation; q and k normed per head with a weight; q grows with the
-    logarithm of the position in steps of `every`."""
+    """Causal softmax attention without rotation (over every earlier token unless a window is given); q and k normed
+    per head with a weight; q grows with the logarithm of the position in steps of `every`."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = rms((h @ t["q"].T).view(T, H, d), eps) * t["q.norm"]
@@ -116,7 +116,8 @@ def qk_normed_attention(h, t, m, eps, alter=()):
     if qt is not None and "no_temp" not in alter:
         p = torch.arange(T, dtype=F)
         q = q * (1.0 + qt["coef"] * torch.log(torch.floor((p + 1) / qt["every"]) + 1.0))[:, None, None]
-    o = softmax_attention(q, k, v, m["scale"], lambda i, j: True)
+    size = None if m.get("mask") is None else m["mask"]["size"] + ("wider" in alter) - ("narrower" in alter)
+    o = softmax_attention(q, k, v, m["scale"], lambda i, j: size is None or i - j < size)
     return o.reshape(T, H * dv) @ t["o"].T
 
 

@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(256) gla_prep_kernel(const T* __restrict__ pro
 }
 
 #define GLA_COLS 16              // value columns of a block
-#define GLA_LANES 8              // lanes that share a column: lane l holds the rows l R .. l R + R - 1
+#define GLA_STAGES 4             // stages of shared memory: chunks copied ahead of the one being walked
 
 __device__ __forceinline__ void gla_cp4(void* smem, const void* gmem) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -59,32 +59,35 @@ __device__ __forceinline__ void gla_cp16(void* smem, const void* gmem) {
 __device__ __forceinline__ void gla_commit() { asm volatile("cp.async.commit_group;"); }
 template <int N> __device__ __forceinline__ void gla_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
 
-// R: rows of a column that a lane holds (dim <= 8 R; the rows beyond dim stay zero).  A stage of shared memory holds
-// `chunk` tokens: [chunk][3][8 R] q', k, alpha, then [chunk][COLS] v; two stages, the next chunk copied (cp.async) while
-// this one is walked.  Per token a lane does S <- alpha S + k v and sums S q over its rows, then the eight lanes of a
-// column add up in a fixed order; only the state's multiply-add is a chain from token to token.
-template <int R>
-__global__ void __launch_bounds__(GLA_COLS * GLA_LANES) gla_scan_kernel(
+// LANES lanes share a column of S; a lane holds R of its rows (dim <= LANES R; the rows beyond dim stay zero): the
+// groups of four rows g = lane + LANES i, so that the lanes of a column read consecutive 16 bytes of a staged row.  A
+// stage of shared memory holds `chunk` tokens: [chunk][3][LANES R] q', k, alpha, then [chunk][COLS] v; four stages, three
+// chunks being copied (cp.async) while one is walked, so that a copy's latency is hidden behind three chunks' arithmetic.
+// Per token a lane does S <- alpha S + k v and sums S q over its rows, then the lanes of a column add up in a fixed
+// order; only the state's multiply-add is a chain from token to token.  Eight lanes a column in the 32-bit path whatever
+// the step's shape (so that its sums keep one order); sixteen where the launch would otherwise leave the GPU idle.
+template <int R, int LANES>
+__global__ void __launch_bounds__(GLA_COLS * LANES) gla_scan_kernel(
     const float* __restrict__ work, long w_ld, float* __restrict__ o, long o_ld, float* __restrict__ state,
     long state_stride, const int* __restrict__ req_start, const int* __restrict__ req_ctx,
     const int* __restrict__ req_qlen, const int* __restrict__ req_slot, int heads, int dim, int vdim, int chunk, int vec4) {
     pdl_wait();
     pdl_trigger();
-    constexpr int DP = R * GLA_LANES;
+    constexpr int DP = R * LANES;
     extern __shared__ __align__(16) float gla_s[];
     const int stage_floats = chunk * (3 * DP + GLA_COLS);
     const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
-    const int tid = threadIdx.x, lane = tid & (GLA_LANES - 1), cl = tid / GLA_LANES;
+    const int tid = threadIdx.x, lane = tid & (LANES - 1), cl = tid / LANES;
     const int col = col0 + cl;
     const bool live = col < vdim;
     const int start = req_start[r], ctx = req_ctx[r], qlen = req_qlen[r];
     const int hd = heads * dim;
-    for (int i = tid; i < 2 * stage_floats; i += blockDim.x) gla_s[i] = 0.0f;      // the padding stays zero
+    for (int i = tid; i < GLA_STAGES * stage_floats; i += blockDim.x) gla_s[i] = 0.0f;      // the padding stays zero
     float* srow = state + (long)req_slot[r] * state_stride + ((long)h * vdim + (live ? col : 0)) * dim;
     float S[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        const int d = lane * R + i;
+        const int d = 4 * (lane + LANES * (i / 4)) + (i & 3);
         S[i] = (ctx > 0 && live && d < dim) ? srow[d] : 0.0f;
     }
     __syncthreads();
@@ -118,50 +121,53 @@ __global__ void __launch_bounds__(GLA_COLS * GLA_LANES) gla_scan_kernel(
         }
         gla_commit();
     };
-    load(0, 0);
+    // one group of copies per chunk, also for chunks beyond the end (empty groups), so that waiting for all but the
+    // last STAGES - 1 groups always means: this chunk has landed
+#pragma unroll
+    for (int p = 0; p < GLA_STAGES - 1; ++p) {
+        if (p * chunk < qlen) load(p, p * chunk); else gla_commit();
+    }
     int stage = 0;
-    for (int c0 = 0; c0 < qlen; c0 += chunk, stage ^= 1) {
+    float* op = o + (long)start * o_ld + (long)h * vdim + col;
+    for (int c0 = 0; c0 < qlen; c0 += chunk, stage = (stage + 1) % GLA_STAGES) {
         const int n_here = min(chunk, qlen - c0);
-        if (c0 + chunk < qlen) {
-            load(stage ^ 1, c0 + chunk);
-            gla_wait<1>();
-        } else {
-            gla_wait<0>();
-        }
+        const int ahead = c0 + (GLA_STAGES - 1) * chunk;
+        // (the stage copied into now was walked in the last round, behind that round's closing barrier)
+        if (ahead < qlen) load((stage + GLA_STAGES - 1) % GLA_STAGES, ahead); else gla_commit();
+        gla_wait<GLA_STAGES - 1>();
         __syncthreads();                                // this chunk has landed
-        const float* st = gla_s + stage * stage_floats;
-        const float* vs = st + chunk * 3 * DP;
-        float* orow = o + (long)(start + c0) * o_ld + (long)h * vdim + col;
+        const float4* row4 = reinterpret_cast<const float4*>(gla_s + stage * stage_floats) + lane;
+        const float* vp = gla_s + stage * stage_floats + chunk * 3 * DP + cl;
 #pragma unroll 4
         for (int tt = 0; tt < n_here; ++tt) {
-            const float4* q4 = reinterpret_cast<const float4*>(st + tt * 3 * DP + lane * R);
-            const float4* k4 = reinterpret_cast<const float4*>(st + tt * 3 * DP + DP + lane * R);
-            const float4* a4 = reinterpret_cast<const float4*>(st + tt * 3 * DP + 2 * DP + lane * R);
-            const float v = vs[tt * GLA_COLS + cl];
-            float acc = 0.0f;
+            const float v = *vp;
+            float acc = 0.0f, acc1 = 0.0f;                  // two partial sums: half as long a chain
 #pragma unroll
             for (int i = 0; i < R / 4; ++i) {
-                const float4 q = q4[i], k = k4[i], a = a4[i];
+                const float4 q = row4[i * LANES], k = row4[DP / 4 + i * LANES], a = row4[2 * (DP / 4) + i * LANES];
                 S[4 * i] = fmaf(a.x, S[4 * i], k.x * v);
                 acc = fmaf(S[4 * i], q.x, acc);
                 S[4 * i + 1] = fmaf(a.y, S[4 * i + 1], k.y * v);
-                acc = fmaf(S[4 * i + 1], q.y, acc);
+                acc1 = fmaf(S[4 * i + 1], q.y, acc1);
                 S[4 * i + 2] = fmaf(a.z, S[4 * i + 2], k.z * v);
                 acc = fmaf(S[4 * i + 2], q.z, acc);
                 S[4 * i + 3] = fmaf(a.w, S[4 * i + 3], k.w * v);
-                acc = fmaf(S[4 * i + 3], q.w, acc);
+                acc1 = fmaf(S[4 * i + 3], q.w, acc1);
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (lane == 0 && live) orow[(long)tt * o_ld] = acc;
+            acc += acc1;
+#pragma unroll
+            for (int off = 1; off < LANES; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+            if (lane == 0 && live) *op = acc;
+            row4 += 3 * (DP / 4);
+            vp += GLA_COLS;
+            op += o_ld;
         }
-        __syncthreads();                                // the stage is rewritten two chunks on
+        __syncthreads();                                // the stage is copied into again in the next round
     }
     if (live)
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-            const int d = lane * R + i;
+            const int d = 4 * (lane + LANES * (i / 4)) + (i & 3);
             if (d < dim) srow[d] = S[i];
         }
 }
@@ -198,25 +204,46 @@ FL_API int fl_gla_prep(const void* proj, int dtype, long ld, const float* w2, co
     return 0;
 }
 
+template <int R, int LANES>
+static int gla_scan_launch(dim3 grid, size_t smem, cudaStream_t stream, const float* work, long w_ld, float* o, long o_ld,
+                           float* state, long state_stride, const int* req_start, const int* req_ctx, const int* req_qlen,
+                           const int* req_slot, int heads, int dim, int vdim, int chunk, int vec4) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<R, LANES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 104 * 1024);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return fl_launch(gla_scan_kernel<R, LANES>, grid, dim3(GLA_COLS * LANES), smem, stream, work, w_ld, o, o_ld, state,
+                     state_stride, req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim, chunk, vec4);
+}
+
+// fixed_order: eight lanes a column whatever the step's shape (the sums of the read-out then keep one order).
 FL_API int fl_gla_scan(const float* work, long w_ld, float* o, long o_ld, float* state, long state_stride,
                        const int* req_start, const int* req_ctx, const int* req_qlen, const int* req_slot, int n_requests,
-                       int heads, int dim, int vdim, cudaStream_t stream) {
+                       int heads, int dim, int vdim, int sms, int fixed_order, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
-    if (dim < 1 || dim > 32 * GLA_LANES || heads > 65535 || (vdim + GLA_COLS - 1) / GLA_COLS > 65535)
+    if (dim < 1 || dim > 256 || heads > 65535 || (vdim + GLA_COLS - 1) / GLA_COLS > 65535)
         return (int)cudaErrorInvalidValue;
-    const int rows = dim <= 4 * GLA_LANES ? 4 : dim <= 8 * GLA_LANES ? 8 : dim <= 16 * GLA_LANES ? 16 : 32;
-    const int chunk = rows <= 8 ? 16 : rows == 16 ? 8 : 4;               // tokens of a stage: two stages within 48 KB
-    const size_t smem = 2 * (size_t)chunk * (3 * rows * GLA_LANES + GLA_COLS) * sizeof(float);
+    const int padded = dim <= 32 ? 32 : dim <= 64 ? 64 : dim <= 128 ? 128 : 256;      // rows of a column, padded
+    const int chunk = padded <= 128 ? 16 : 8;                            // tokens of a stage
+    const size_t smem = GLA_STAGES * (size_t)chunk * (3 * padded + GLA_COLS) * sizeof(float);   // <= 103 KB
     // 16-byte copies where every source address is a multiple of 16 bytes
     const int vec4 = dim % 4 == 0 && vdim % 4 == 0 && w_ld % 4 == 0 && ((uintptr_t)work % 16) == 0;
     dim3 grid(n_requests, heads, (vdim + GLA_COLS - 1) / GLA_COLS);
-#define FL_GLA_SCAN(R)                                                                                                  \
-    return fl_launch(gla_scan_kernel<R>, grid, dim3(GLA_COLS * GLA_LANES), smem, stream, work, w_ld, o, o_ld, state,    \
-                     state_stride, req_start, req_ctx, req_qlen, req_slot, heads, dim, vdim, chunk, vec4)
-    if (rows == 4) { FL_GLA_SCAN(4); }
-    if (rows == 8) { FL_GLA_SCAN(8); }
-    if (rows == 16) { FL_GLA_SCAN(16); }
-    FL_GLA_SCAN(32);
+    const bool wide = !fixed_order && padded >= 64 && (long)grid.x * grid.y * grid.z < 2L * sms;
+#define FL_GLA_SCAN(R, L)                                                                                               \
+    return gla_scan_launch<R, L>(grid, smem, stream, work, w_ld, o, o_ld, state, state_stride, req_start, req_ctx,      \
+                                 req_qlen, req_slot, heads, dim, vdim, chunk, vec4)
+    if (wide) {
+        if (padded == 64) { FL_GLA_SCAN(4, 16); }
+        if (padded == 128) { FL_GLA_SCAN(8, 16); }
+        FL_GLA_SCAN(16, 16);
+    }
+    if (padded == 32) { FL_GLA_SCAN(4, 8); }
+    if (padded == 64) { FL_GLA_SCAN(8, 8); }
+    if (padded == 128) { FL_GLA_SCAN(16, 8); }
+    FL_GLA_SCAN(32, 8);
 #undef FL_GLA_SCAN
 }
 

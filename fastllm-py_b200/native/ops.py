@@ -903,18 +903,22 @@ def gla_prep(proj, w2, b2, work, heads, dim, vdim, rank, q_scale, tau):
               vdim, rank, float(q_scale), float(tau), _stream()), "gla_prep")
 
 
-def gla_scan(work, o, state, step, heads, dim, vdim):
+def gla_scan(work, o, state, step, heads, dim, vdim, fixed_order=False):
     """Per request and head S <- diag(alpha) S + k v^T, o = S^T q over the step's tokens; q | k | alpha | v are the
     float32 columns of `work`, `o` float32 [N, heads * vdim]; state rows [heads, vdim, dim] float32 are read (unless
-    the request starts) and written."""
+    the request starts) and written.  `fixed_order`: the read-out's sum keeps one order whatever the step's shape
+    (otherwise a lone prompt spreads a column over more lanes than a batch does)."""
     _require_cuda(work, o, state)
     if work.dtype != torch.float32 or o.dtype != torch.float32 or state.dtype != torch.float32:
         raise KernelError("gla_scan: work, o and state must be float32")
+    sms = _sm_counts.get(work.device)
+    if sms is None:
+        sms = _sm_counts[work.device] = torch.cuda.get_device_properties(work.device).multi_processor_count
     fn = _fn("gla", "fl_gla_scan", [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_void_p, c_void_p, c_void_p,
-                                    c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+                                    c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(work), _ld(work), _ptr(o), _ld(o), _ptr(state), state.stride(0), _ptr(step.req_start),
-              _ptr(step.req_ctx), _ptr(step.req_qlen), _ptr(step.req_slot), step.n_requests, heads, dim, vdim, _stream()),
-           "gla_scan")
+              _ptr(step.req_ctx), _ptr(step.req_qlen), _ptr(step.req_slot), step.n_requests, heads, dim, vdim, sms,
+              int(fixed_order), _stream()), "gla_scan")
 
 
 def gla_gated_norm(o, gate, weight, out, heads, vdim, eps):

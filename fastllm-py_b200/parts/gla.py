@@ -81,7 +81,8 @@ class GatedLinearAttention(Part):
         work = ws.rows("gla_work", n, 3 * self.hd + self.hv, torch.float32)
         ops.gla_prep(proj, self.a2, self.a2_bias, work, self.heads, self.dim, self.vdim, self.rank, self.q_scale, self.tau)
         o = ws.rows("gla_o", n, self.hv, torch.float32)
-        ops.gla_scan(work, o, cache.tensor, step, self.heads, self.dim, self.vdim)
+        ops.gla_scan(work, o, cache.tensor, step, self.heads, self.dim, self.vdim,
+                     fixed_order=dt == torch.float32)     # the 32-bit path: cuts and batches agree bit for bit
         y = ws.rows("gla_y", n, self.hv, dt)
         ops.gla_gated_norm(o, proj[:, 2 * self.hd + self.hv:2 * self.hd + 2 * self.hv], self.norm_w, y, self.heads,
                            self.vdim, self.norm_eps)

@@ -5,19 +5,34 @@
 //                   the variance as the mean of the squared deviations (two passes over the row, which waits in shared
 //                   memory); with `rows` only those rows are normed and x is not written back
 //   rms_mix         out = weight * (a / rms(a) * wa + b / rms(b) * wb): two mixers' results, each normed over the
-//                   width, averaged
+//                   width, averaged (`dtype` is the type of out and of whichever of a and b is a tensor)
 //   scaled_add      x += scale * delta
 //   activation      out = f(x, 1) for the gated units' f (relu squared among them): a feed-forward without a gate
 //
+// A sum that waits as the split-K partial sums of the product that made it (`splits` float slabs, `split_stride`
+// floats apart, rows `ld` apart) is added up in slab order while it is read, in float, without a kernel of its own.
+//
 // All arithmetic is float; a row's sums depend on the row alone.
 #include "common.cuh"
+
+// Element `idx` of a tensor of T, or (splits > 0) of the float slabs behind the same pointer, added in slab order.
+template <typename T>
+__device__ __forceinline__ float nm_read(const T* p, long idx, int splits, long split_stride) {
+    if (splits > 0) {
+        const float* f = reinterpret_cast<const float*>(p);
+        float sum = f[idx];
+        for (int k = 1; k < splits; ++k) sum += f[(long)k * split_stride + idx];
+        return sum;
+    }
+    return to_f32<T>(p[idx]);
+}
 
 template <typename TD, typename TW, typename TO>
 __global__ void __launch_bounds__(256) add_layernorm_kernel(float* __restrict__ x, long x_ld, const TD* __restrict__ delta,
                                                             long d_ld, float scale, const TW* __restrict__ w,
                                                             const TW* __restrict__ b, TO* __restrict__ out, long out_ld,
                                                             int dim, float eps, const int* __restrict__ rows,
-                                                            int write_back) {
+                                                            int write_back, int splits, long split_stride) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float ln_row[];                   // [dim]
@@ -29,7 +44,7 @@ __global__ void __launch_bounds__(256) add_layernorm_kernel(float* __restrict__ 
     for (int i = threadIdx.x; i < dim; i += blockDim.x) {
         float v = xr[i];
         if (delta != nullptr) {
-            v += scale * to_f32<TD>(delta[src * d_ld + i]);
+            v += scale * nm_read<TD>(delta, src * d_ld + i, splits, split_stride);
             if (write_back) xr[i] = v;
         }
         ln_row[i] = v;
@@ -48,47 +63,53 @@ __global__ void __launch_bounds__(256) add_layernorm_kernel(float* __restrict__ 
 
 FL_API int fl_add_layernorm(float* x, long x_ld, const void* delta, int d_dtype, long d_ld, float scale, const void* w,
                             const void* b, int w_dtype, void* out, int out_dtype, long out_ld, int n_rows, int dim,
-                            float eps, const int* rows, cudaStream_t stream) {
+                            float eps, const int* rows, int splits, long split_stride, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if ((size_t)dim * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if ((size_t)dim * sizeof(float) > 48 * 1024 || (splits > 0 && d_dtype != FL_F32)) return (int)cudaErrorInvalidValue;
     const int write_back = rows ? 0 : 1;
     FL_DISPATCH(d_dtype, TD, FL_DISPATCH(w_dtype, TW, FL_DISPATCH(out_dtype, TO,
         return fl_launch(add_layernorm_kernel<TD, TW, TO>, dim3(n_rows), dim3(256), (size_t)dim * sizeof(float), stream, x,
                          x_ld, (const TD*)delta, d_ld, scale, (const TW*)w, (const TW*)b, (TO*)out, out_ld, dim, eps, rows,
-                         write_back))));
+                         write_back, splits, split_stride))));
     return 0;
 }
 
 template <typename T, typename TW>
 __global__ void __launch_bounds__(256) rms_mix_kernel(const T* __restrict__ a, long a_ld, const T* __restrict__ b, long b_ld,
                                                       const TW* __restrict__ wa, const TW* __restrict__ wb, T* __restrict__ out,
-                                                      long out_ld, int dim, float eps, float weight) {
+                                                      long out_ld, int dim, float eps, float weight, int a_splits,
+                                                      long a_stride, int b_splits, long b_stride) {
     pdl_wait();
     pdl_trigger();
+    extern __shared__ float mix_row[];                  // [2][dim]: both rows, read (and added up) once
     __shared__ float scratch[32];
     const long r = blockIdx.x;
     float sa = 0.0f, sb = 0.0f;
     for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-        const float va = to_f32<T>(a[r * a_ld + i]), vb = to_f32<T>(b[r * b_ld + i]);
+        const float va = nm_read<T>(a, r * a_ld + i, a_splits, a_stride), vb = nm_read<T>(b, r * b_ld + i, b_splits, b_stride);
+        mix_row[i] = va;
+        mix_row[dim + i] = vb;
         sa += va * va;
         sb += vb * vb;
     }
     const float ia = 1.0f / sqrtf(block_sum(sa, scratch) / (float)dim + eps);
     const float ib = 1.0f / sqrtf(block_sum(sb, scratch) / (float)dim + eps);
     for (int i = threadIdx.x; i < dim; i += blockDim.x) {
-        const float va = to_f32<T>(a[r * a_ld + i]) * ia * to_f32<TW>(wa[i]);
-        const float vb = to_f32<T>(b[r * b_ld + i]) * ib * to_f32<TW>(wb[i]);
+        const float va = mix_row[i] * ia * to_f32<TW>(wa[i]);
+        const float vb = mix_row[dim + i] * ib * to_f32<TW>(wb[i]);
         out[r * out_ld + i] = from_f32<T>(weight * (va + vb));
     }
 }
 
 FL_API int fl_rms_mix(const void* a, long a_ld, const void* b, long b_ld, int dtype, const void* wa, const void* wb,
-                      int w_dtype, void* out, long out_ld, int n_rows, int dim, float eps, float weight,
-                      cudaStream_t stream) {
+                      int w_dtype, void* out, long out_ld, int n_rows, int dim, float eps, float weight, int a_splits,
+                      long a_stride, int b_splits, long b_stride, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if ((size_t)dim * 2 * sizeof(float) > 48 * 1024) return (int)cudaErrorInvalidValue;
     FL_DISPATCH(dtype, T, FL_DISPATCH(w_dtype, TW,
-        return fl_launch(rms_mix_kernel<T, TW>, dim3(n_rows), dim3(256), 0, stream, (const T*)a, a_ld, (const T*)b, b_ld,
-                         (const TW*)wa, (const TW*)wb, (T*)out, out_ld, dim, eps, weight)));
+        return fl_launch(rms_mix_kernel<T, TW>, dim3(n_rows), dim3(256), (size_t)dim * 2 * sizeof(float), stream, (const T*)a,
+                         a_ld, (const T*)b, b_ld, (const TW*)wa, (const TW*)wb, (T*)out, out_ld, dim, eps, weight, a_splits,
+                         a_stride, b_splits, b_stride)));
     return 0;
 }
 

@@ -814,28 +814,48 @@ def head_gate(x, gate, heads, vdim):
 
 # ----------------------------------------------- layer norm, mixes, activation
 
+def _summand(x):
+    """(pointer, row pitch, splits, floats between slabs, dtype code) of a tensor, or of split-K partial sums (an
+    object with data, splits, split_stride, ld and check()) that a kernel adds up while it reads."""
+    if x is None:
+        return None, 0, 0, 0, F32
+    if isinstance(x, torch.Tensor):
+        return _ptr(x), _ld(x), 0, 0, dtype_code(x)
+    x.check()
+    return _ptr(x.data), x.ld, x.splits, x.split_stride, F32
+
+
 def add_layernorm(resid, delta, scale, weight, bias, out, eps, rows=None):
-    """resid += scale * delta (float32, written back unless rows are gathered; delta None: nothing to add);
-    out = (resid - mean) / sqrt(var + eps) * weight + bias."""
-    _require_cuda(resid, delta, weight, bias, out, rows)
+    """resid += scale * delta (float32, written back unless rows are gathered; delta None: nothing to add; delta may
+    be split-K partial sums, added up while they are read); out = (resid - mean) / sqrt(var + eps) * weight + bias."""
+    _require_cuda(resid, weight, bias, out, rows)
     if resid.dtype != torch.float32 or (bias is not None and bias.dtype != weight.dtype):
         raise KernelError("add_layernorm: the residual stream is float32; weight and bias share a dtype")
+    d_ptr, d_ld, splits, stride, d_code = _summand(delta)
     fn = _fn("norm_mix", "fl_add_layernorm", [c_void_p, c_long, c_void_p, c_int, c_long, c_float, c_void_p, c_void_p, c_int,
-                                              c_void_p, c_int, c_long, c_int, c_int, c_float, c_void_p, c_void_p])
-    _check(fn(_ptr(resid), _ld(resid), _ptr(delta), F32 if delta is None else dtype_code(delta),
-              0 if delta is None else _ld(delta), float(scale), _ptr(weight), _ptr(bias), dtype_code(weight), _ptr(out),
-              dtype_code(out), _ld(out), out.shape[0], resid.shape[1], float(eps), _ptr(rows), _stream()), "add_layernorm")
+                                              c_void_p, c_int, c_long, c_int, c_int, c_float, c_void_p, c_int, c_long,
+                                              c_void_p])
+    _check(fn(_ptr(resid), _ld(resid), d_ptr, d_code, d_ld, float(scale), _ptr(weight), _ptr(bias), dtype_code(weight),
+              _ptr(out), dtype_code(out), _ld(out), out.shape[0], resid.shape[1], float(eps), _ptr(rows), splits, stride,
+              _stream()), "add_layernorm")
 
 
 def rms_mix(a, b, w_a, w_b, out, eps, weight=0.5):
-    """out = weight * (a / rms(a) * w_a + b / rms(b) * w_b), row by row."""
-    _require_cuda(a, b, w_a, w_b, out)
-    if a.dtype != b.dtype or a.dtype != out.dtype or w_a.dtype != w_b.dtype:
-        raise KernelError("rms_mix: a, b and out share a dtype, and so do the weights")
+    """out = weight * (a / rms(a) * w_a + b / rms(b) * w_b), row by row.  a and b are tensors of out's dtype or
+    split-K partial sums, added up while they are read."""
+    _require_cuda(w_a, w_b, out)
+    for x in (a, b):
+        if isinstance(x, torch.Tensor) and x.dtype != out.dtype:
+            raise KernelError("rms_mix: a, b and out share a dtype")
+    if w_a.dtype != w_b.dtype:
+        raise KernelError("rms_mix: the weights share a dtype")
+    a_ptr, a_ld, a_splits, a_stride, _ = _summand(a)
+    b_ptr, b_ld, b_splits, b_stride, _ = _summand(b)
     fn = _fn("norm_mix", "fl_rms_mix", [c_void_p, c_long, c_void_p, c_long, c_int, c_void_p, c_void_p, c_int, c_void_p,
-                                        c_long, c_int, c_int, c_float, c_float, c_void_p])
-    _check(fn(_ptr(a), _ld(a), _ptr(b), _ld(b), dtype_code(a), _ptr(w_a), _ptr(w_b), dtype_code(w_a), _ptr(out), _ld(out),
-              a.shape[0], a.shape[1], float(eps), float(weight), _stream()), "rms_mix")
+                                        c_long, c_int, c_int, c_float, c_float, c_int, c_long, c_int, c_long, c_void_p])
+    _check(fn(a_ptr, a_ld, b_ptr, b_ld, dtype_code(out), _ptr(w_a), _ptr(w_b), dtype_code(w_a), _ptr(out), _ld(out),
+              out.shape[0], out.shape[1], float(eps), float(weight), a_splits, a_stride, b_splits, b_stride, _stream()),
+           "rms_mix")
 
 
 def scaled_add(resid, delta, scale):

@@ -136,7 +136,8 @@ class ResidualStream:
         """`norm.apply(self, out, rows)`, with a pending sum that the norm can take."""
         pending = self.pending
         if pending is not None and not isinstance(pending, torch.Tensor):
-            both = getattr(norm, "takes_partial", False) and self.pending_scale == 1.0 and \
+            both = getattr(norm, "takes_partial", False) and \
+                (self.pending_scale == 1.0 or getattr(norm, "takes_scale", False)) and \
                 (self.pending_norm is None or getattr(norm, "takes_post_norm", False))
             if rows is not None or not both:
                 pending = self.pending = pending.reduce_into(self.spill())

@@ -88,6 +88,7 @@ class LayerNorm(Part):
     category = "norm"
     native_libraries = ("norm_mix",)
     takes_scale = True                   # the pending sum times a number: added while the row is read
+    takes_partial = True                 # split-K partial sums are added while the row is read
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
@@ -108,8 +109,9 @@ class LayerNorm(Part):
             self.bias = tensors["bias"].to(self.weight.dtype).contiguous()
 
     def apply(self, stream, out, rows=None):
-        """Norm the residual stream into `out`, adding the pending sum (a tensor: `ResidualStream.norm_into` sees to
-        it) first.  With `rows` only those rows are normed, into out[0..m), and the pending sum stays pending."""
+        """Norm the residual stream into `out`, adding the pending sum (a tensor, or split-K partial sums) first.
+        With `rows` only those rows are normed, into out[0..m), and the pending sum (a tensor then:
+        `ResidualStream.norm_into` sees to it) stays pending."""
         ops.add_layernorm(stream.x, stream.pending, stream.pending_scale, self.weight, self.bias, out, self.eps, rows)
         if rows is None:
             stream.pending, stream.pending_scale = None, 1.0

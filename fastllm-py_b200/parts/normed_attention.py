@@ -39,6 +39,8 @@ class NormedAttention(Part):
     category = "mixer"
     native_libraries = ("sink_attention",)
     SCRATCH = "sink attention splits"
+    honours_partial_side = True          # with `partial_side` set, the last product's partial sums go to the second scratch
+    partial_side = False
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
@@ -124,9 +126,10 @@ class NormedAttention(Part):
         return [ops.sink_tc_library(self.dim, self.vdim)] if self._tc() else []
 
     def reserve(self, limits):
-        for lin in (self.proj, self.o):
-            if lin is not None:
-                lin.reserve(self.ctx.dtype, limits.max_tokens)
+        if self.proj is not None:
+            self.proj.reserve(self.ctx.dtype, limits.max_tokens)
+        if self.o is not None:
+            self.o.reserve(self.ctx.dtype, limits.max_tokens, side=self.partial_side)
         if self._tc():
             from ..native.build import load_library
             load_library(*ops.sink_tc_library(self.dim, self.vdim))        # built now, not inside the first step
@@ -201,4 +204,4 @@ class NormedAttention(Part):
                                     self.sink, cache.page_size, chunk=self.chunk)
         if self.gated:
             ops.head_gate(ctx, proj[:, self.q_cols + self.k_cols + self.v_cols:], self.heads, self.vdim)
-        return self.o.forward(ctx, out, defer=True)
+        return self.o.forward(ctx, out, defer=True, side=self.partial_side)

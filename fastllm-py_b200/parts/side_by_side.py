@@ -5,8 +5,10 @@ their results, each first normed over the model width.
 
 Each of the two is a mixer part of its own with whatever cache or state it needs; this part asks the
 cache manager for both (`cache_needs`) and hands each its view.  Either may leave its last product as
-split-K partial sums; they are added up into this part's buffers before the other's products run (the
-scratch for partial sums is one buffer), and one kernel norms both rows and mixes them.
+split-K partial sums, which the one kernel that norms both rows and mixes them adds up as it reads.
+The scratch for partial sums is one buffer and a second one beside it: a left mixer that says
+`honours_partial_side` is told (`partial_side = True`) to leave its sums in the second, where the right
+mixer's products do not overwrite them; one that does not gets its sums added up before the right runs.
 """
 from __future__ import annotations
 
@@ -31,6 +33,8 @@ class SideBySide(Part):
         self.weight = float(p.get("weight", 0.5))
         self.left = build_part("mixer", p["left"], ctx)
         self.right = build_part("mixer", p["right"], ctx)
+        if getattr(self.left, "honours_partial_side", False):
+            self.left.partial_side = True
         self.w_left = self.w_right = None
 
     def children(self):
@@ -73,8 +77,8 @@ class SideBySide(Part):
             buf = ws.rows(f"side_{side}", n, self.hidden, dt)
             part = getattr(self, side)
             left = part.forward(h, buf, step, None if cache is None else cache.get(side))
-            if left is not None:
-                left.reduce_into(buf)
-            results.append(buf)
+            if left is not None and side == "left" and not getattr(part, "partial_side", False):
+                left = left.reduce_into(buf)             # the right mixer's products would overwrite the sums
+            results.append(buf if left is None else left)
         ops.rms_mix(results[0], results[1], self.w_left, self.w_right, out, self.norm_eps, self.weight)
         return None

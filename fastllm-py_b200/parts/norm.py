@@ -89,6 +89,8 @@ class LayerNorm(Part):
     native_libraries = ("norm_mix",)
     takes_scale = True                   # the pending sum times a number: added while the row is read
     takes_partial = True                 # split-K partial sums are added while the row is read
+    PARTIAL_FROM = 64                    # ... in steps of this many rows and more: one block reads a row's slabs, which
+                                         # for a handful of rows is slower than the reduce kernel's many blocks
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
@@ -112,6 +114,9 @@ class LayerNorm(Part):
         """Norm the residual stream into `out`, adding the pending sum (a tensor, or split-K partial sums) first.
         With `rows` only those rows are normed, into out[0..m), and the pending sum (a tensor then:
         `ResidualStream.norm_into` sees to it) stays pending."""
+        if stream.pending is not None and not isinstance(stream.pending, torch.Tensor) and \
+                stream.x.shape[0] < self.PARTIAL_FROM:
+            stream.pending = stream.pending.reduce_into(stream.spill())
         ops.add_layernorm(stream.x, stream.pending, stream.pending_scale, self.weight, self.bias, out, self.eps, rows)
         if rows is None:
             stream.pending, stream.pending_scale = None, 1.0

@@ -24,6 +24,7 @@ class SideBySide(Part):
     category = "mixer"
     native_libraries = ("norm_mix",)
     SIDES = ("left", "right")
+    PARTIAL_FROM = 64                    # rows from which the mix kernel adds partial sums up itself
 
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
@@ -77,8 +78,11 @@ class SideBySide(Part):
             buf = ws.rows(f"side_{side}", n, self.hidden, dt)
             part = getattr(self, side)
             left = part.forward(h, buf, step, None if cache is None else cache.get(side))
-            if left is not None and side == "left" and not getattr(part, "partial_side", False):
-                left = left.reduce_into(buf)             # the right mixer's products would overwrite the sums
+            if left is not None and (n < self.PARTIAL_FROM or
+                                     (side == "left" and not getattr(part, "partial_side", False))):
+                # a handful of rows: the reduce kernel's many blocks are faster than one block a row; a left mixer
+                # that used the first scratch buffer: the right mixer's products would overwrite the sums
+                left = left.reduce_into(buf)
             results.append(buf if left is None else left)
         ops.rms_mix(results[0], results[1], self.w_left, self.w_right, out, self.norm_eps, self.weight)
         return None

@@ -20,6 +20,7 @@
 #include "common.cuh"
 
 // work row: q' (heads x dim) | k (heads x dim) | alpha (heads x dim) | v (heads x vdim), float.
+// w2: the decay's second matrix transposed, [rank][heads x dim], so that neighbouring threads read neighbouring floats.
 template <typename T>
 __global__ void __launch_bounds__(256) gla_prep_kernel(const T* __restrict__ proj, long ld, const float* __restrict__ w2,
                                                        const float* __restrict__ b2, float* __restrict__ work, long w_ld,
@@ -33,16 +34,16 @@ __global__ void __launch_bounds__(256) gla_prep_kernel(const T* __restrict__ pro
     for (int i = threadIdx.x; i < rank; i += blockDim.x) low_s[i] = to_f32<T>(row[2 * hd + 2 * hv + i]);
     __syncthreads();
     float* w = work + t * w_ld;
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    // (blockIdx.y shares a token's columns out over blocks: a handful of tokens alone would leave the GPU idle)
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < hd; i += gridDim.y * blockDim.x) {
         w[i] = to_f32<T>(row[i]) * q_scale;
         w[hd + i] = to_f32<T>(row[hd + i]);
         float z = b2[i];
-        const float* wr = w2 + (long)i * rank;
-        for (int k = 0; k < rank; ++k) z += wr[k] * low_s[k];
+        for (int k = 0; k < rank; ++k) z += w2[(long)k * hd + i] * low_s[k];       // w2 is stored [rank][heads x dim]
         const float logsig = fminf(z, 0.0f) - log1pf(expf(-fabsf(z)));
         w[2 * hd + i] = expf(logsig / tau);
     }
-    for (int i = threadIdx.x; i < hv; i += blockDim.x) w[3 * hd + i] = to_f32<T>(row[2 * hd + i]);
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < hv; i += gridDim.y * blockDim.x) w[3 * hd + i] = to_f32<T>(row[2 * hd + i]);
 }
 
 #define GLA_COLS 16              // value columns of a block
@@ -198,7 +199,9 @@ FL_API int fl_gla_prep(const void* proj, int dtype, long ld, const float* w2, co
                        int n_tokens, int heads, int dim, int vdim, int rank, float q_scale, float tau, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rank < 1 || (size_t)rank * sizeof(float) > 48 * 1024 || !(tau > 0.0f)) return (int)cudaErrorInvalidValue;
-    FL_DISPATCH(dtype, T, return fl_launch(gla_prep_kernel<T>, dim3(n_tokens), dim3(256), (size_t)rank * sizeof(float), stream,
+    int share = n_tokens >= 256 ? 1 : (heads * dim + 255) / 256;
+    if (share > 16) share = 16;
+    FL_DISPATCH(dtype, T, return fl_launch(gla_prep_kernel<T>, dim3(n_tokens, share), dim3(256), (size_t)rank * sizeof(float), stream,
                                            (const T*)proj, ld, w2, b2, work, w_ld, heads, dim, vdim, rank, q_scale,
                                            tau));
     return 0;

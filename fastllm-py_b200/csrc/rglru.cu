@@ -132,6 +132,60 @@ __global__ void __launch_bounds__(256) rglru_gates_kernel(const float* __restric
         }
 }
 
+// The same for a handful of tokens (single tokens of a few requests), where a thread an output would leave the GPU
+// idle behind a few long walks: one warp per output channel, the lanes sharing the row, eight tokens a block.  Its sums
+// run in another order than the kernel's above, so the 32-bit path, whose results must not depend on what else is in the
+// step, never takes it.
+#define RG_FEW 8
+template <typename TW>
+__global__ void __launch_bounds__(256) rglru_gates_few_kernel(const float* __restrict__ u, long u_ld, const TW* __restrict__ w_a,
+                                                              const TW* __restrict__ w_i, const float* __restrict__ b_a,
+                                                              const float* __restrict__ b_i, const float* __restrict__ rate,
+                                                              float* __restrict__ a_out, float* __restrict__ b_out, long o_ld,
+                                                              int n_tokens, int width, int bw) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ __align__(16) float u_s[];        // [RG_FEW][bw]
+    const int t0 = blockIdx.x * RG_FEW, b = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_here = min(RG_FEW, n_tokens - t0);
+    for (int i = threadIdx.x; i < RG_FEW * bw; i += blockDim.x) {
+        const int tt = i / bw, k = i - tt * bw;
+        u_s[i] = tt < n_here ? u[(long)(t0 + tt) * u_ld + b * bw + k] : 0.0f;
+    }
+    __syncthreads();
+    for (int o = blockIdx.z * 8 + warp; o < bw; o += gridDim.z * 8) {
+        const TW* ra = w_a + ((long)b * bw + o) * bw;
+        const TW* ri = w_i + ((long)b * bw + o) * bw;
+        float sa[RG_FEW], si[RG_FEW];
+#pragma unroll
+        for (int tt = 0; tt < RG_FEW; ++tt) sa[tt] = si[tt] = 0.0f;
+        for (int k = lane; k < bw; k += 32) {
+            const float wa = to_f32<TW>(ra[k]), wi = to_f32<TW>(ri[k]);
+#pragma unroll
+            for (int tt = 0; tt < RG_FEW; ++tt) {
+                sa[tt] = fmaf(wa, u_s[tt * bw + k], sa[tt]);
+                si[tt] = fmaf(wi, u_s[tt * bw + k], si[tt]);
+            }
+        }
+        float mine_a = 0.0f, mine_i = 0.0f;
+#pragma unroll
+        for (int tt = 0; tt < RG_FEW; ++tt) {
+            const float ta = warp_sum(sa[tt]), ti = warp_sum(si[tt]);
+            if (lane == tt) { mine_a = ta; mine_i = ti; }
+        }
+        if (lane < n_here) {
+            const int c = b * bw + o;
+            const float r = 1.0f / (1.0f + expf(-(mine_a + b_a[c])));
+            const float g = 1.0f / (1.0f + expf(-(mine_i + b_i[c])));
+            const float log_a = rate[c] * r;
+            const long at = (long)(t0 + lane) * o_ld + c;
+            a_out[at] = expf(log_a);
+            b_out[at] = sqrtf(-expm1f(2.0f * log_a)) * g * u_s[lane * bw + o];
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128) rglru_scan_kernel(
     const float* __restrict__ a, const float* __restrict__ bx, long ab_ld, const T* __restrict__ proj, long ld,
@@ -252,7 +306,15 @@ FL_API int fl_rglru(const void* proj, int dtype, long ld, const float* bias, con
     FL_DISPATCH(w_dtype, TW, rc = fl_launch(rglru_gates_kernel<TW, VEC>, ggrid, dim3(threads), smem, stream,           \
                                             (const float*)u, s_ld, (const TW*)w_a, (const TW*)w_i, b_a, b_i, rate, a, bx, \
                                             s_ld, n_tokens, width, bw))
-    if (vec) { FL_RG_GATES(true); } else { FL_RG_GATES(false); }
+    if (!fixed_order && n_tokens < 64) {                // a handful of tokens: a warp an output
+        int z = (bw + 7) / 8;
+        const int few_tiles = (n_tokens + RG_FEW - 1) / RG_FEW;
+        while (z > 1 && (long)few_tiles * blocks * z > 1024) z = (z + 1) / 2;
+        FL_DISPATCH(w_dtype, TW, rc = fl_launch(rglru_gates_few_kernel<TW>, dim3(few_tiles, blocks, z), dim3(256),
+                                                (size_t)RG_FEW * bw * sizeof(float), stream, (const float*)u, s_ld,
+                                                (const TW*)w_a, (const TW*)w_i, b_a, b_i, rate, a, bx, s_ld, n_tokens,
+                                                width, bw));
+    } else if (vec) { FL_RG_GATES(true); } else { FL_RG_GATES(false); }
 #undef FL_RG_GATES
     if (rc) return rc;
     if (!fixed_order && n_tokens > 32 * n_requests) {   // prompt portions: the tokens of a request side by side

@@ -123,7 +123,8 @@ __global__ void __launch_bounds__(256) head_prep_kernel(
     float* buf = prep_s + warp * dim;
     float factor = 1.0f;
     if (temp_every > 0) factor = 1.0f + temp_coef * logf((float)((pos + 1) / temp_every) + 1.0f);
-    for (int idx = warp; idx < heads + kv_heads; idx += 8) {
+    // (a block's eight warps take eight of the token's heads; blockIdx.y counts the eights)
+    for (int idx = blockIdx.y * 8 + warp; idx < heads + kv_heads; idx += gridDim.y * 8) {
         const bool is_q = idx < heads;
         const int col0 = is_q ? idx * dim : nq + (idx - heads) * dim;
         T* krow = dst + (long)(idx - heads) * head_stride;
@@ -165,7 +166,7 @@ __global__ void __launch_bounds__(256) head_prep_kernel(
     }
     if (!v_from_k) {
         const int nv = kv_heads * vdim;
-        for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+        for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < nv; i += gridDim.y * blockDim.x) {
             const int g = i / vdim, d = i - g * vdim;
             dst[g * head_stride + dim + d] = from_f32<T>(to_f32<T>(row[nq + nk + i]) + (bias ? bias[nq + nk + i] : 0.0f));
         }
@@ -179,10 +180,11 @@ FL_API int fl_head_prep(const void* proj, int dtype, long ld, const float* bias,
                         long page_stride, int page_size, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (norm_mode < 0 || norm_mode > 2 || rot < 0 || rot > dim || (rot & 1) || (rot > 0 && (cos_t == nullptr || sin_t == nullptr)) ||
-        (v_from_k && vdim != dim) || (size_t)dim * 8 * sizeof(float) > 48 * 1024 || cache == nullptr)
+        (v_from_k && vdim != dim) || (size_t)dim * 8 * sizeof(float) > 48 * 1024 || cache == nullptr ||
+        (heads + kv_heads + 7) / 8 > 65535)
         return (int)cudaErrorInvalidValue;
     FL_DISPATCH(dtype, T, FL_DISPATCH(q_dtype, TQ,
-        return fl_launch(head_prep_kernel<T, TQ>, dim3(n_tokens), dim3(256), (size_t)dim * 8 * sizeof(float), stream,
+        return fl_launch(head_prep_kernel<T, TQ>, dim3(n_tokens, (heads + kv_heads + 7) / 8), dim3(256), (size_t)dim * 8 * sizeof(float), stream,
                          (const T*)proj, ld, bias, q_w, k_w, norm_mode, eps, rot, interleaved, cos_t, sin_t, positions,
                          temp_coef, temp_every, v_from_k, (TQ*)q_out, q_ld, heads, kv_heads, dim, vdim, slots, (T*)cache,
                          page_stride, page_size)));

@@ -913,10 +913,12 @@ def rglru(proj, bias, conv_w, conv_b, w_a, w_i, b_a, b_i, rate, state, step, u, 
 
 def gla_prep(proj, w2, b2, work, heads, dim, vdim, rank, q_scale, tau):
     """proj columns q | k (heads x dim each) | v | gate (heads x vdim each) | low (rank): q times `q_scale`, k, the decay
-    alpha = sigmoid(W_2 low + b_2)^(1 / tau) per key channel and v into the float32 columns q | k | alpha | v of `work`."""
+    alpha = sigmoid(W_2 low + b_2)^(1 / tau) per key channel and v into the float32 columns q | k | alpha | v of `work`.
+    `w2` is W_2 transposed: [rank, heads * dim]."""
     _require_cuda(proj, w2, b2, work)
-    if work.dtype != torch.float32 or w2.dtype != torch.float32 or b2.dtype != torch.float32 or not w2.is_contiguous():
-        raise KernelError("gla_prep: the work buffer, W_2 and b_2 are float32")
+    if work.dtype != torch.float32 or w2.dtype != torch.float32 or b2.dtype != torch.float32 or not w2.is_contiguous() \
+            or tuple(w2.shape) != (rank, heads * dim):
+        raise KernelError("gla_prep: the work buffer, W_2 (transposed: [rank, heads * dim]) and b_2 are float32")
     fn = _fn("gla", "fl_gla_prep", [c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_long, c_int, c_int, c_int, c_int,
                                     c_int, c_float, c_float, c_void_p])
     _check(fn(_ptr(proj), dtype_code(proj), _ld(proj), _ptr(w2), _ptr(b2), _ptr(work), _ld(work), proj.shape[0], heads, dim,

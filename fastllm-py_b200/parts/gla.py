@@ -63,7 +63,7 @@ class GatedLinearAttention(Part):
             raise ValueError("gated_linear_attention: the projections must be stored in one dtype")
         self.proj = Linear(mats)
         self.o = Linear([tensors["o"]])
-        self.a2 = tensors["a2"].float().contiguous()
+        self.a2 = tensors["a2"].float().t().contiguous()               # [rank, heads * dim]: the kernel reads along heads * dim
         self.a2_bias = tensors["a2_bias"].float().contiguous()
         self.norm_w = tensors["norm"].contiguous()
 

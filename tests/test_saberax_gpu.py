@@ -580,7 +580,7 @@ def test_recurrence_and_linear_attention_kernels_over_three_steps(dtype):
         work = torch.empty(n, 3 * hd + hv, device="cuda")
         o = torch.empty(n, hv, device="cuda")
         y = torch.empty(n, hv, dtype=dtype, device="cuda")
-        ops.gla_prep(pg, f32(t_g["a2"]), f32(t_g["a2.b"]), work, heads, dim, vdim, rank, dim ** -0.5, tau)
+        ops.gla_prep(pg, f32(t_g["a2"].T), f32(t_g["a2.b"]), work, heads, dim, vdim, rank, dim ** -0.5, tau)
         ops.gla_scan(work, o, state_g, step, heads, dim, vdim)
         ops.gla_gated_norm(o, pg[:, 2 * hd + hv:2 * hd + 2 * hv], f32(t_g["norm"]), y, heads, vdim, 1e-5)
         for i, e in enumerate(entries):

@@ -10,7 +10,8 @@
 // A request's state row is [S (width) | the last taps - 1 rows of x_pre (width each)], float; it is read unless the
 // request starts (context 0) and written at the end of the step.
 //
-//   rglru_conv    per (token, channel): u, from the step's rows of the same request and the kept rows before them
+//   rglru_conv    per (token, channel): u, from the step's rows of the same request and the kept rows before them; four
+//                 channels a thread where the pitches allow 16-byte accesses
 //   rglru_gates   per (16 tokens, block): both block products on the CUDA cores in float, one thread an output channel,
 //                 then a and the input term
 //   rglru_scan    per (request, channel): the recurrence over the request's tokens in order, the gate branch, the new
@@ -46,6 +47,51 @@ __global__ void __launch_bounds__(256) rglru_conv_kernel(
         acc += conv_w[(long)c * taps + j] * x;
     }
     u[(long)t * u_ld + c] = acc;
+}
+
+// Four channels a thread (width a multiple of 4, rows 8-byte aligned): the same sums, each channel's taps in order.
+__device__ __forceinline__ void rg_load4(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void rg_load4(const bf16* p, float* v) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) rglru_conv4_kernel(
+    const T* __restrict__ proj, long ld, const float* __restrict__ bias, const float* __restrict__ conv_w,
+    const float* __restrict__ conv_b, const float* __restrict__ state, long state_stride, const int* __restrict__ tok_req,
+    const int* __restrict__ positions, const int* __restrict__ req_start, const int* __restrict__ req_ctx,
+    const int* __restrict__ req_slot, float* __restrict__ u, long u_ld, int width, int taps) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+    if (c >= width) return;
+    const int r = tok_req[t], pos = positions[t];
+    const int start = req_start[r], ctx = req_ctx[r];
+    const float* tail = state + (long)req_slot[r] * state_stride + width;
+    float xb[4], acc[4];
+    rg_load4(bias + width + c, xb);
+    rg_load4(conv_b + c, acc);
+    for (int j = 0; j < taps; ++j) {
+        const int p = pos - (taps - 1) + j;
+        if (p < 0) continue;
+        float x[4];
+        if (p >= ctx) {
+            rg_load4(proj + (long)(start + p - ctx) * ld + width + c, x);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) x[e] += xb[e];
+        } else {
+            rg_load4(tail + (long)(p - ctx + taps - 1) * width + c, x);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] += conv_w[(long)(c + e) * taps + j] * x[e];
+    }
+    *reinterpret_cast<float4*>(u + (long)t * u_ld + c) = make_float4(acc[0], acc[1], acc[2], acc[3]);
 }
 
 #define RG_TT 16                 // tokens of a block of rglru_gates
@@ -294,9 +340,19 @@ FL_API int fl_rglru(const void* proj, int dtype, long ld, const float* bias, con
     const size_t smem = (size_t)RG_TT * bw * sizeof(float);
     if (smem > 48 * 1024 || blocks > 65535) return (int)cudaErrorInvalidValue;
     int rc = 0;
-    FL_DISPATCH(dtype, T, rc = fl_launch(rglru_conv_kernel<T>, dim3(n_tokens, (width + 255) / 256), dim3(256), 0, stream,
-                                         (const T*)proj, ld, bias, conv_w, conv_b, (const float*)state, state_stride,
-                                         tok_req, positions, req_start, req_ctx, req_slot, u, s_ld, width, taps));
+    const bool four = width % 4 == 0 && ld % 4 == 0 && s_ld % 4 == 0 && state_stride % 4 == 0 && ((uintptr_t)proj % 16) == 0 &&
+                      ((uintptr_t)u % 16) == 0 && ((uintptr_t)state % 16) == 0 && ((uintptr_t)bias % 16) == 0 &&
+                      ((uintptr_t)conv_b % 16) == 0;
+    if (four) {
+        FL_DISPATCH(dtype, T, rc = fl_launch(rglru_conv4_kernel<T>, dim3(n_tokens, (width / 4 + 255) / 256), dim3(256), 0,
+                                             stream, (const T*)proj, ld, bias, conv_w, conv_b, (const float*)state,
+                                             state_stride, tok_req, positions, req_start, req_ctx, req_slot, u, s_ld, width,
+                                             taps));
+    } else {
+        FL_DISPATCH(dtype, T, rc = fl_launch(rglru_conv_kernel<T>, dim3(n_tokens, (width + 255) / 256), dim3(256), 0, stream,
+                                             (const T*)proj, ld, bias, conv_w, conv_b, (const float*)state, state_stride,
+                                             tok_req, positions, req_start, req_ctx, req_slot, u, s_ld, width, taps));
+    }
     if (rc) return rc;
     const int tiles = (n_tokens + RG_TT - 1) / RG_TT;
     const int threads = bw >= 256 ? 256 : ((bw + 31) / 32) * 32;

@@ -665,3 +665,84 @@ def test_recurrence_in_segments_equals_token_by_token():
     assert float((seq_out - seg_out).abs().max()) <= 0.02 * float(seq_out.abs().max())
     assert float((seq_state - seg_state).abs().max()) <= 1e-5 * max(1.0, float(seq_state.abs().max()))
     assert float(seq_state[1, :width].abs().max()) > 0                      # slot 1 carried its state in and out
+
+
+def _drawn_model(rng):
+    """A configuration drawn at random: layer kinds in any order, layers on another layer's tensors, sizes from lists
+    that hold the awkward ones (one head, twelve query heads a key/value head, keys of 72, blocks of 13, one tap)."""
+    ch = rng.choice
+    width, vocab = ch([24, 40, 64, 136]), rng.randint(50, 200)
+
+    def sizes():
+        kv, group = ch([1, 2, 3]), ch([1, 1, 2, 3, 4, 12])
+        return kv * group, kv, ch([8, 12, 16, 24, 32, 48, 64, 72])
+
+    def rotation(dim, yarn):
+        if rng.random() < 0.2:
+            return None, None
+        scaling = None
+        if rng.random() < 0.6:
+            scaling = (ch([2.0, 4.0, 32.0]), ch([16, 64, 1024]), ch([8.0, 32.0]), ch([0.5, 1.0])) if yarn else \
+                (ch([2.0, 8.0]), ch([16, 64, 512]), ch([0.5, 1.0]), ch([2.0, 4.0]))
+        return 2 * rng.randint(1, dim // 2), scaling
+
+    def mlp():
+        r = rng.random()
+        if r < 0.2:
+            return None
+        if r < 0.5:
+            return st.dense(ch([16, 30, 64]))
+        experts = ch([4, 6, 8, 12, 16])
+        top = rng.randint(1, min(experts, 5))
+        groups = None
+        if rng.random() < 0.6:
+            count = ch([g for g in (1, 2, 3, 4, 6, 8) if experts % g == 0])
+            keep = rng.randint(1, count)
+            if keep * (experts // count) >= top:
+                groups = (count, keep)
+        return st.moe(experts, top, ch([8, 16, 32]), ch([0.5, 1.0, 2.5]), groups, ch([None, 8, 24]))
+
+    layers, own = [], []
+    for _ in range(rng.randint(3, 6)):
+        if own and rng.random() < 0.2:
+            layers.append(ch(own))
+            continue
+        kind = ch(["parallel", "parallel_2", "attention"])
+        heads, kv, dim = sizes()
+        scale, mask = ch([dim ** -0.5, 0.1, 0.3]), ch([None, 1, 2, 5, 17, 33])
+        if kind == "attention":
+            dims, scaling = rotation(dim, False)
+            mixer = st.chunked(heads, kv, dim, chunk=mask, rot=dims, base=ch([500.0, 250000.0]), scaling=scaling, scale=scale)
+        elif kind == "parallel":
+            bw, blocks = ch([4, 8, 13, 16, 32]), ch([1, 2, 3, 5])
+            temp = None if rng.random() < 0.3 else (ch([0.1, 0.3, -0.1]), ch([1, 4, 16]))
+            mixer = st.pair(st.normed(heads, kv, dim, ch([4, 8, 24, 48, 100]), q_temp=temp, scale=scale),
+                            st.recurrent(bw * blocks, blocks, ch([1, 2, 4, 7])))
+        else:
+            dims, scaling = rotation(dim, True)
+            mixer = st.pair(st.windowed(heads, kv, dim, ch([4, 8, 24, 48, 100]), window=mask, rot=dims, base=ch([500.0, 50000.0]),
+                                        scaling=scaling, scale=scale),
+                            st.linear_attention(ch([1, 2, 3]), ch([4, 8, 20, 32, 64, 100]), ch([4, 12, 16, 32, 80]), ch([1.0, 4.0, 64.0])))
+        own.append(len(layers))
+        layers.append((mixer, mlp()))
+    return st.config(layers, vocab, width, ch([1e-5, 1e-6]), ch([0.7, 1.0, 0.35])), ch([1, 3, 8, 33])
+
+
+@pytest.mark.parametrize("seed", [0, 3, 10, 11])
+def test_configurations_drawn_at_random(tmp_path, seed):
+    import random
+
+    rng = random.Random(seed)
+    raw, rank = _drawn_model(rng)
+    w = st.weights(raw, seed=seed, rank=rank)
+    requests = {f"q{i}": np.random.default_rng(seed + i).integers(0, raw["vocab"], size=n).tolist()
+                for i, n in enumerate([rng.randint(1, 45) for _ in range(3)])}
+    want = {rid: plain.forward(raw, w, toks).float() for rid, toks in requests.items()}
+    folder = st.write(raw, w, tmp_path / "m")
+    steps = replay.mixed(requests, live=2, seed=seed, prefill_sizes=(9, 2, 17, 5), decode_tail=6)
+    top = max(float(v.abs().max()) for v in want.values())
+    got = replay.run_in_process(load(folder, "float32", page=8, tokens=replay.peak_tokens(steps, 8) + 8), steps)
+    assert worst(got, want) <= 2e-4 * max(1.0, top), raw
+    got = replay.run_in_process(load(folder, "bfloat16", page=8, tokens=replay.peak_tokens(steps, 8) + 8), steps)
+    errs = np.array([float((got[k] - want[k[0]][k[1]]).pow(2).mean().sqrt()) for k in got])
+    assert np.median(errs) <= 0.08 * float(torch.cat([v.flatten() for v in want.values()]).std()), raw

@@ -76,11 +76,9 @@ def make_plan(cfg: SaberaxConfig, tensor_names=None, tensor_shapes=None) -> Mode
     def norm(name):
         return PartSpec("layernorm", dict(size=width, eps=eps), {"weight": name, "bias": name + ".b"})
 
-    layers, order, plan_index = [], [], {}
-    for i, layer in enumerate(cfg.layers):
-        if layer.weights_of is not None:
-            continue
-        base, m = f"l{i}.", layer.mixer
+    def layer_spec(i, layer, base):
+        """The parts of one layer whose tensors are named from `base` (its own `l<i>.`, or another layer's)."""
+        m = layer.mixer
         mx = base + "mix."
         if isinstance(m, PairConfig):
             mixer = PartSpec("side_by_side",
@@ -117,10 +115,22 @@ def make_plan(cfg: SaberaxConfig, tensor_names=None, tensor_shapes=None) -> Mode
             else:
                 raise ValueError(f"layer {i}: unknown feed-forward configuration {f!r}")
             norms["feed_forward"] = norm(base + "norm2")
-        plan_index[i] = len(layers)
-        layers.append(LayerSpec("prenorm", mixer, ff, norms, params=dict(residual_scale=cfg.residual_mult)))
+        return LayerSpec("prenorm", mixer, ff, norms, params=dict(residual_scale=cfg.residual_mult))
+
+    def same(a, b):
+        return (a.type, a.mixer, a.mlp) == (b.type, b.mixer, b.mlp)
+
+    layers, order, plan_index = [], [], {}
     for i, layer in enumerate(cfg.layers):
-        order.append(LayerRun(plan_index[i if layer.weights_of is None else layer.weights_of]))
+        source = layer.weights_of
+        if source is not None and same(layer, cfg.layers[source]):
+            continue                                     # runs the source's parts again, with a cache of its own
+        # a layer with tensors of its own; or one on another layer's tensors whose constants (a window, say) differ
+        # from that layer's: parts of its own over the same tensors
+        plan_index[i] = len(layers)
+        layers.append(layer_spec(i, layer, f"l{i if source is None else source}."))
+    for i, layer in enumerate(cfg.layers):
+        order.append(LayerRun(plan_index[i] if i in plan_index else plan_index[layer.weights_of]))
     io = dict(vocab_size=cfg.vocab, hidden_size=width)
     return ModelPlan(
         hidden_size=width, vocab_size=cfg.vocab, max_positions=DEFAULT_MAX_POSITIONS,

@@ -286,8 +286,9 @@ class SaberaxConfig:
             if j >= len(layers) or j == i or layers[j].weights_of is not None:
                 raise ConfigError(f"config.json: layers[{i}].weights_of {j} must name another layer with tensors "
                                   f"of its own")
-            if (layers[j].type, layers[j].mixer, layers[j].mlp) != (layer.type, layer.mixer, layer.mlp):
-                raise ConfigError(f"config.json: layers[{i}] uses the tensors of layers[{j}] but differs from it")
+            if layers[j].type != layer.type or (layers[j].mlp is None) != (layer.mlp is None):
+                raise ConfigError(f"config.json: layers[{i}] uses the tensors of layers[{j}] but is a layer of another "
+                                  f"kind")
         norm = KeyReader(_sub(raw, "norm", "config"))
         return cls(vocab=r.integer("vocab"), width=r.integer("width"), norm_eps=norm.number("eps"),
                    residual_mult=r.number("residual_mult", default=1.0, positive=False), layers=tuple(layers))

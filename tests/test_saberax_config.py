@@ -76,7 +76,7 @@ def test_cache_needs_follow_the_layers():
     (("layers", 1, "mlp", "kind"), "sparse", "kind"),
     (("layers", 0, "mlp", "ff"), None, "ff"),
     (("layers", 3, "weights_of"), 3, "weights_of"),
-    (("layers", 3, "weights_of"), 1, "differs"),
+    (("layers", 3, "weights_of"), 1, "another kind"),
     (("width",), "wide", "width"),
 ])
 def test_wrong_values_are_refused_by_name(path, value, word):
@@ -172,3 +172,19 @@ def test_routing_oracle_keeps_to_the_groups_with_the_best_pairs():
         differs += kept != set(pick.view(50, 4, 3).max(dim=-1).values[t].topk(2).indices.tolist())
     assert differs > 0                                     # the sum of two is not the best one
     assert torch.allclose(w.sum(dim=-1), torch.full((50,), 2.5, dtype=torch.float64))
+
+
+def test_a_layer_on_anothers_tensors_may_differ_in_its_constants():
+    """The same tensors under another window: parts of its own over the same names, a run of its own."""
+    raw = st.config([(st.pair(st.windowed(2, 1, 8, 8, window=4, rot=8), st.linear_attention(2, 4, 6, 4.0)), st.dense(16)), 0],
+                    width=24, vocab=30)
+    raw["layers"][1]["mixer"]["left"]["mask"]["size"] = 9
+    cfg, dec = decoder(raw)
+    assert cfg.to_hf() == raw and len(dec.blocks) == 2 and [run.layer for run in dec.order] == [0, 1]
+    assert dec.expected_tensors() == st.tensor_shapes(raw)
+    assert dec.blocks[0].mixer.left.window == 4 and dec.blocks[1].mixer.left.window == 9
+    w = st.weights(raw, seed=2)
+    toks = list(range(2, 22))
+    same = copy.deepcopy(raw)
+    same["layers"][1]["mixer"]["left"]["mask"]["size"] = 4
+    assert float((plain.forward(raw, w, toks) - plain.forward(same, w, toks)).abs().max()) > 1e-4

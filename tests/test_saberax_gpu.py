@@ -746,3 +746,22 @@ def test_configurations_drawn_at_random(tmp_path, seed):
     got = replay.run_in_process(load(folder, "bfloat16", page=8, tokens=replay.peak_tokens(steps, 8) + 8), steps)
     errs = np.array([float((got[k] - want[k[0]][k[1]]).pow(2).mean().sqrt()) for k in got])
     assert np.median(errs) <= 0.08 * float(torch.cat([v.flatten() for v in want.values()]).std()), raw
+
+
+def test_a_layer_on_anothers_tensors_with_a_window_of_its_own(tmp_path):
+    """The same tensors under another window and chunk: the engine gives each such layer parts of its own."""
+    raw = st.config([(st.pair(st.windowed(2, 1, 8, 8, window=4, rot=8, scale=1.2), st.linear_attention(2, 4, 6, 4.0)), st.dense(16)),
+                     (st.chunked(2, 2, 8, chunk=5, rot=4, scale=1.2), st.moe(4, 2, 8, 2.0, shared=8)), 0, 1], width=24, vocab=30)
+    raw["layers"][2]["mixer"]["left"]["mask"]["size"] = 9
+    raw["layers"][3]["mixer"]["mask"]["size"] = 11
+    w = st.weights(raw, seed=2)
+    folder = st.write(raw, w, tmp_path / "m")
+    toks = np.random.default_rng(3).integers(0, 30, size=40).tolist()
+    want = plain.forward(raw, w, toks).float()
+    got = replay.run_in_process(load(folder, "float32"), replay.portions({"a": toks}, (7, 2, 11)))
+    err = worst(got, {"a": want})
+    assert err <= 2e-4 * float(want.abs().max())
+    same = copy.deepcopy(raw)
+    same["layers"][2]["mixer"]["left"]["mask"]["size"] = 4
+    same["layers"][3]["mixer"]["mask"]["size"] = 5
+    assert float((plain.forward(same, w, toks).float() - want).abs().max()) > 100 * max(err, 1e-5)
